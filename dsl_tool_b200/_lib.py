@@ -1,0 +1,160 @@
+"""ctypes binding of libdslgemm.so (the C ABI declared in include/dslgemm.h).
+
+There is no fallback of any kind: if the library is missing or a CUDA device is absent,
+the operators raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Dict, Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("DSLGEMM_LIBRARY", os.path.join(_HERE, "libdslgemm.so"))
+
+# enums of include/dslgemm.h
+F32, BF16, F16 = 0, 1, 2
+FP8_PER_TENSOR, FP8_GROUP_1X128, FP8_BLOCK_128X128 = 0, 1, 2
+FP4_NV, FP4_MX = 0, 1
+MAX_GROUPS = 1024
+
+_ERR_NAMES = {
+    -1: "a required pointer is NULL",
+    -2: "bad shape (negative, too large, or not a multiple the format needs)",
+    -3: "pointer or leading dimension not 16-byte aligned",
+    -4: "unknown dtype / mode / format",
+    -5: "the CUDA driver's tensor-map encoder is unavailable or refused the descriptor",
+    -6: "beyond a fixed capacity of the library",
+}
+_STATUS_NAMES = {1: "TMA producer wait timed out", 2: "MMA issuer wait timed out",
+                 4: "epilogue wait timed out", 8: "self-test wait timed out"}
+
+
+class Epilogue(ctypes.Structure):
+    _fields_ = [
+        ("scale_a_host", ctypes.c_float),
+        ("scale_b_host", ctypes.c_float),
+        ("scale_a_dev", ctypes.c_void_p),
+        ("scale_b_dev", ctypes.c_void_p),
+        ("row_scale", ctypes.c_void_p),
+        ("col_scale", ctypes.c_void_p),
+        ("out_dtype", ctypes.c_int),
+    ]
+
+
+_lib: Optional[ctypes.CDLL] = None
+_lock = threading.Lock()
+
+_vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+_SIGNATURES = {
+    "dsl_version": (ctypes.c_char_p, []),
+    "dsl_sf_bytes": (ctypes.c_size_t, [_ll, _ll]),
+    "dsl_sf_bytes_grouped": (ctypes.c_size_t, [_ll, _ll, _i]),
+    "dsl_quant_fp8": (_i, [_vp, _i, _ll, _ll, _i, _vp, _i, _vp, _vp, _vp]),
+    "dsl_quant_fp4": (_i, [_vp, _i, _ll, _ll, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp]),
+    "dsl_transpose_u8": (_i, [_vp, _vp, _i, _i, _vp]),
+    "dsl_gemm_fp8": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_gemm_fp8_groupwise": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i, _vp, _i,
+                                    ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_gemm_fp4": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i, _vp, _i,
+                          ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        f"{LIB_PATH} not found: build it with `python -m dsl_tool_b200.build` "
+                        "(there is no fallback path)")
+                cdll = ctypes.CDLL(LIB_PATH)
+                for name, (res, args) in _SIGNATURES.items():
+                    fn = getattr(cdll, name)
+                    fn.restype = res
+                    fn.argtypes = args
+                _lib = cdll
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise ValueError(f"{what}: {_ERR_NAMES.get(rc, 'invalid argument')} (code {rc})")
+    raise RuntimeError(f"{what}: CUDA error {rc}")
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("the 'cuda' backend needs a CUDA device (sm_100a); there is no CPU fallback")
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("all tensors must live on a CUDA device; there is no CPU fallback")
+        if dev is not None and t.device != dev:
+            raise ValueError("tensors live on different devices")
+        dev = t.device
+    return dev
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}[dt]
+    except KeyError:
+        raise TypeError(f"unsupported input dtype {dt}; use float32, bfloat16 or float16") from None
+
+
+_status: Dict[int, torch.Tensor] = {}
+_scratch: Dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device status word the kernels OR their give-up bits into."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[idx] = t
+    return t
+
+
+def scratch_word(device: torch.device) -> torch.Tensor:
+    """Per-device 16-byte scratch (tensor amax cell)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _scratch.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=device)
+        _scratch[idx] = t
+    return t
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel since the last check gave up on a wait."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = status_word(device)
+    torch.cuda.synchronize(device)
+    v = int(word.item())
+    if v != 0:
+        word.zero_()
+        what = ", ".join(n for b, n in _STATUS_NAMES.items() if v & b)
+        raise RuntimeError(f"a GEMM kernel gave up on a barrier wait ({what}; status {v})")

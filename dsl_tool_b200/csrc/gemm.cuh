@@ -1,0 +1,45 @@
+// Kernel argument block and host launchers of the tcgen05 GEMM kernels (gemm.cu, gemm_groupwise.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "dslgemm.h"
+
+namespace dsl {
+
+enum { KIND_F8 = 0, KIND_NVF4 = 1, KIND_MXF4 = 2, KIND_BF16 = 3 };
+
+struct GemmArgs {
+    int m_total;                 // rows of A / C over all row groups
+    int n;                       // columns of C (rows of each group's weight)
+    int k_bytes;                 // bytes per operand row: K for FP8, K/2 for FP4, 2K for BF16
+    int num_groups;
+    const int* group_offsets;    // device int32[num_groups+1] row offsets, or nullptr (one group of m_total rows)
+    const uint8_t* sfa;          // tiled block scales of A / B (FP4 kinds)
+    const uint8_t* sfb;
+    int sf_katoms;               // 512-byte scale tiles along K per 128 rows = ceil(nblk/4)
+    int sfb_tiles_per_group;     // ceil(n/128)
+    const float* gsa;            // FP8 groupwise: A scales [m_total, K/128]
+    const float* gsb;            //                B scales (see sb_block)
+    int sb_block;                // 1: [G, ceil(n/128), K/128] block scales, 0: [G, K/128, n] per column
+    float s1, s2;                // epilogue scales (host values) ...
+    const float* s1_dev;         // ... overridden by these device scalars when non-null
+    const float* s2_dev;
+    int scale_product;           // 1: multiply by (s1*s2) once; 0: (acc*s1)*s2
+    const float* row_scale;
+    const float* col_scale;
+    void* c;
+    long long ldc;
+    int out_bf16;
+    int band;                    // column tiles per raster band (L2 reuse)
+    uint32_t* status;
+};
+
+int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);
+int launch_gemm_fp8_groupwise(const void* A, const void* B, GemmArgs args, cudaStream_t st);
+int launch_bounded_wait_selftest(uint32_t* status, unsigned limit_us, cudaStream_t st);
+bool make_tmap_u8(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box0,
+                  uint32_t box1);
+
+}  // namespace dsl

@@ -1,0 +1,415 @@
+// Activation / weight quantise + scale-pack kernels (HBM-bound; one vectorised pass over
+// the input, 16 elements per thread, packed 8/16-byte stores).
+//
+// Arithmetic is IEEE fp32 throughout (explicit __fdiv_rn / __frcp_rn / __fmul_rn, never
+// fast-math) so that the bytes are identical to the CPU oracle's:
+//   FP8  : scale = max(amax/448, 1e-12), q = e4m3_rn_satfinite(x / scale)
+//          (rule of the reference quantiser, cuda/gemm/fp8_gemm.cu:119-144), applied per
+//          tensor, per 1x128 K-group, or per 128x128 block.
+//   NVFP4: gs = amax_tensor/2688 (1 if zero); sf = ue4m3(min((amax16/6)/gs, 448));
+//          inv = 1/(f32(sf)*gs) (0 if that product is below FLT_MIN); q = e2m1_rn(x*inv).
+//   MXFP4: e = clamp(exponent(amax32) - 2, -127, 127); byte = e+127; q = e2m1_rn(x * 2^-e).
+// FP4 nibble order follows cuda/gemm/fp4_gemm.cu:46,88: low nibble = even element.
+// Scale bytes are written straight into the 512-byte (128 rows x 4 K-blocks) tile layout the
+// block-scaled MMA consumes: byte (r, c) of a tile at (r%32)*16 + (r/32)*4 + c.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <float.h>
+
+#include "ptx.cuh"
+#include "quant.cuh"
+
+namespace dsl {
+
+// ---- 16-element vector loads ------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float (&v)[16]);
+
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
+    const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float4 t = __ldg(q + i);
+        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+    }
+}
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[16]) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 t = __ldg(q + i);
+        uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+            v[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+        }
+    }
+}
+template <>
+__device__ __forceinline__ void load16<__half>(const __half* p, float (&v)[16]) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 t = __ldg(q + i);
+        uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float2 f = __half22float2(*reinterpret_cast<__half2*>(&w[j]));
+            v[8 * i + 2 * j] = f.x;
+            v[8 * i + 2 * j + 1] = f.y;
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+
+__device__ __forceinline__ float amax16(const float (&v)[16]) {
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+    return m;
+}
+__device__ __forceinline__ float fp8_scale_from_amax(float amax) {
+    float s = __fdiv_rn(amax, 448.0f);
+    return s < 1e-12f ? 1e-12f : s;
+}
+__device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t lo = cvt_e4m3x2(__fdiv_rn(v[4 * i], s), __fdiv_rn(v[4 * i + 1], s));
+        uint32_t hi = cvt_e4m3x2(__fdiv_rn(v[4 * i + 2], s), __fdiv_rn(v[4 * i + 3], s));
+        w[i] = lo | (hi << 16);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ uint2 quant16_e2m1(const float (&v)[16], float inv) {
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        uint32_t b = cvt_e2m1x2(__fmul_rn(v[2 * i], inv), __fmul_rn(v[2 * i + 1], inv));
+        w[i >> 2] |= b << (8 * (i & 3));
+    }
+    return make_uint2(w[0], w[1]);
+}
+
+// ---- tensor amax -------------------------------------------------------------------------
+// Non-negative floats order like their bit patterns, so the reduction is an integer
+// atomicMax (same trick as cuda/gemm/fp8_gemm.cu:132) and the result is order-independent.
+template <typename T>
+__global__ void __launch_bounds__(256) amax_kernel(const T* __restrict__ x, size_t n, uint32_t* amax_bits) {
+    float m = 0.f;
+    const size_t nvec = n / 16;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        float v[16];
+        load16<T>(x + i * 16, v);
+        m = fmaxf(m, amax16(v));
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (size_t i = nvec * 16; i < n; ++i) m = fmaxf(m, fabsf(to_f32<T>(x[i])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane_id() == 0 && m > 0.f) atomicMax(amax_bits, __float_as_uint(m));
+}
+
+__global__ void nvfp4_global_scale_kernel(const uint32_t* amax_bits, float* gs) {
+    float a = __uint_as_float(*amax_bits);
+    *gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
+}
+
+// ---- FP8 ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_fp8_tensor_kernel(const T* __restrict__ x, size_t n, const uint32_t* amax_bits, float* scale_io,
+                        uint8_t* __restrict__ q) {
+    float s;
+    if (amax_bits != nullptr) {
+        s = fp8_scale_from_amax(__uint_as_float(*amax_bits));
+        if (blockIdx.x == 0 && threadIdx.x == 0) *scale_io = s;
+    } else {
+        s = *scale_io;
+    }
+    const size_t nvec = n / 16;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        float v[16];
+        load16<T>(x + i * 16, v);
+        *reinterpret_cast<uint4*>(q + i * 16) = quant16_e4m3(v, s);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (size_t i = nvec * 16; i < n; ++i)
+            q[i] = static_cast<uint8_t>(cvt_e4m3x2(__fdiv_rn(to_f32<T>(x[i]), s), 0.f) & 0xFFu);
+}
+
+// 1 x 128 groups along K: 8 threads per group, 16 elements each.  K % 16 == 0.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_fp8_1x128_kernel(const T* __restrict__ x, long long M, int K, uint8_t* __restrict__ q,
+                       float* __restrict__ scales) {
+    const int ng = (K + 127) / 128;
+    const long long total = M * ng;
+    const long long gthread = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const long long gid = gthread >> 3;
+    const int j = static_cast<int>(gthread & 7);
+    long long row = 0;
+    int kg = 0;
+    bool valid = gid < total;
+    if (valid) {
+        row = gid / ng;
+        kg = static_cast<int>(gid - row * ng);
+        valid = kg * 128 + j * 16 < K;
+    }
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    const size_t off = static_cast<size_t>(row) * K + kg * 128 + j * 16;
+    if (valid) load16<T>(x + off, v);
+    float m = amax16(v);
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+    const float s = fp8_scale_from_amax(m);
+    if (valid) *reinterpret_cast<uint4*>(q + off) = quant16_e4m3(v, s);
+    if (j == 0 && gid < total) scales[gid] = s;
+}
+
+// 128 x 128 blocks of a K-major [N, K] weight: one CTA per block, 64 elements per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quant_fp8_block128_kernel(const T* __restrict__ w, int N, int K, uint8_t* __restrict__ q,
+                          float* __restrict__ scales) {
+    __shared__ float red[8];
+    const int kb = blockIdx.x, nb = blockIdx.y;
+    const int r = nb * 128 + (threadIdx.x >> 1);
+    const int k0 = kb * 128 + (threadIdx.x & 1) * 64;
+    float v[4][16];
+    float m = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[c][i] = 0.f;
+        if (r < N && k0 + c * 16 < K) load16<T>(w + static_cast<size_t>(r) * K + k0 + c * 16, v[c]);
+        m = fmaxf(m, amax16(v[c]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane_id() == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i]);
+    const float s = fp8_scale_from_amax(m);
+    if (threadIdx.x == 0) scales[static_cast<size_t>(nb) * gridDim.x + kb] = s;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (r < N && k0 + c * 16 < K)
+            *reinterpret_cast<uint4*>(q + static_cast<size_t>(r) * K + k0 + c * 16) = quant16_e4m3(v[c], s);
+}
+
+// ---- FP4 ---------------------------------------------------------------------------------
+constexpr int kMaxGroups = 1024;
+
+// Where the scale byte of (row, K-block) goes.  With ragged row groups every group starts at
+// a fresh 128-row tile (tile index = number of 128-row tiles of the groups before it).
+struct SfIndexer {
+    const int* offs;   // shared-memory copy of the group offsets [G+1], or nullptr
+    const int* tile0;  // shared-memory first tile of each group [G+1]
+    int groups;
+    int katoms;
+    __device__ __forceinline__ size_t operator()(long long row, int blk) const {
+        long long tile;
+        int rin;
+        if (offs == nullptr) {
+            tile = row >> 7;
+            rin = static_cast<int>(row & 127);
+        } else {
+            int lo = 0, hi = groups;   // last g with offs[g] <= row
+            while (hi - lo > 1) {
+                int mid = (lo + hi) >> 1;
+                if (offs[mid] <= row) lo = mid; else hi = mid;
+            }
+            int rl = static_cast<int>(row - offs[lo]);
+            tile = tile0[lo] + (rl >> 7);
+            rin = rl & 127;
+        }
+        return (static_cast<size_t>(tile) * katoms + (blk >> 2)) * 512 + (rin & 31) * 16 + (rin >> 5) * 4 + (blk & 3);
+    }
+};
+
+template <typename T, int FMT>   // FMT 0: NVFP4 (block 16, UE4M3 + global scale)  1: MXFP4 (block 32, E8M0)
+__global__ void __launch_bounds__(256)
+quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __restrict__ gs_ptr,
+                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
+                 int num_groups) {
+    __shared__ int s_offs[kMaxGroups + 1];
+    __shared__ int s_tile0[kMaxGroups + 1];
+    SfIndexer sfi;
+    const int nblk = FMT == 0 ? K / 16 : K / 32;
+    sfi.katoms = (nblk + 3) / 4;
+    sfi.groups = num_groups;
+    sfi.offs = nullptr;
+    sfi.tile0 = nullptr;
+    if (group_offsets != nullptr) {
+        for (int g = threadIdx.x; g <= num_groups; g += blockDim.x) s_offs[g] = group_offsets[g];
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int g = 0; g < num_groups; ++g) {
+                s_tile0[g] = t;
+                t += (s_offs[g + 1] - s_offs[g] + 127) >> 7;
+            }
+            s_tile0[num_groups] = t;
+        }
+        __syncthreads();
+        sfi.offs = s_offs;
+        sfi.tile0 = s_tile0;
+    }
+    const int cpr = K / 16;   // 16-element chunks per row
+    const long long total = M * cpr;
+    const long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const bool valid = id < total;
+    long long row = 0;
+    int kc = 0;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    if (valid) {
+        row = id / cpr;
+        kc = static_cast<int>(id - row * cpr);
+        load16<T>(x + static_cast<size_t>(id) * 16, v);
+    }
+    float m = amax16(v);
+    float inv;
+    uint32_t sfb;
+    int blk;
+    bool writer;
+    if (FMT == 0) {
+        const float gs = *gs_ptr;
+        float t = __fdiv_rn(__fdiv_rn(m, 6.0f), gs);
+        t = fminf(t, 448.0f);
+        sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
+        const float d = __fmul_rn(e4m3_to_float(sfb), gs);
+        inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+        blk = kc;
+        writer = true;
+    } else {
+        m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));   // cpr is even, so lane pairs share a row
+        int e = static_cast<int>((__float_as_uint(m) >> 23) & 0xFFu) - 129;
+        e = e < -127 ? -127 : e;
+        sfb = static_cast<uint32_t>(e + 127);
+        inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+        blk = kc >> 1;
+        writer = (kc & 1) == 0;
+    }
+    if (valid) {
+        *reinterpret_cast<uint2*>(q + static_cast<size_t>(id) * 8) = quant16_e2m1(v, inv);
+        if (writer) sf[sfi(row, blk)] = static_cast<uint8_t>(sfb);
+    }
+}
+
+// ---- byte-matrix transpose ([R, C] -> [C, R]), used to turn a [K, N] weight K-major --------
+__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
+                                                           int R, int C) {
+    __shared__ uint8_t tile[64][65];
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        int r = i >> 6, c = i & 63;
+        tile[r][c] = (r0 + r < R && c0 + c < C) ? in[static_cast<size_t>(r0 + r) * C + c0 + c] : 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        int c = i >> 6, r = i & 63;
+        if (r0 + r < R && c0 + c < C) out[static_cast<size_t>(c0 + c) * R + r0 + r] = tile[r][c];
+    }
+}
+
+// ---- host launchers ------------------------------------------------------------------------
+static inline int grid_for(size_t work_items, int per_block, int cap) {
+    size_t g = (work_items + per_block - 1) / per_block;
+    if (g < 1) g = 1;
+    return static_cast<int>(g > static_cast<size_t>(cap) ? cap : g);
+}
+
+template <typename T>
+static cudaError_t quant_fp8_typed(const T* x, long long rows, long long cols, int mode, float* scale_io,
+                                   int scale_given, uint8_t* q, uint32_t* ws, cudaStream_t st) {
+    const size_t n = static_cast<size_t>(rows) * cols;
+    if (mode == DSL_FP8_PER_TENSOR) {
+        const int grid = grid_for(n / 16, 256, 148 * 16);
+        if (!scale_given) {
+            cudaError_t e = cudaMemsetAsync(ws, 0, 4, st);
+            if (e != cudaSuccess) return e;
+            amax_kernel<T><<<grid, 256, 0, st>>>(x, n, ws);
+        }
+        quant_fp8_tensor_kernel<T><<<grid, 256, 0, st>>>(x, n, scale_given ? nullptr : ws, scale_io, q);
+    } else if (mode == DSL_FP8_GROUP_1X128) {
+        const long long threads = rows * ((cols + 127) / 128) * 8;
+        const long long grid = (threads + 255) / 256;
+        if (grid > 0)
+            quant_fp8_1x128_kernel<T><<<static_cast<unsigned>(grid), 256, 0, st>>>(x, rows, static_cast<int>(cols), q, scale_io);
+    } else {
+        dim3 grid(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>((rows + 127) / 128));
+        if (grid.x > 0 && grid.y > 0)
+            quant_fp8_block128_kernel<T><<<grid, 256, 0, st>>>(x, static_cast<int>(rows), static_cast<int>(cols), q, scale_io);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quant_fp8(const void* x, int dtype, long long rows, long long cols, int mode, float* scale_io,
+                             int scale_given, uint8_t* q, uint32_t* ws, cudaStream_t st) {
+    switch (dtype) {
+        case DSL_F32: return quant_fp8_typed(static_cast<const float*>(x), rows, cols, mode, scale_io, scale_given, q, ws, st);
+        case DSL_BF16: return quant_fp8_typed(static_cast<const __nv_bfloat16*>(x), rows, cols, mode, scale_io, scale_given, q, ws, st);
+        default: return quant_fp8_typed(static_cast<const __half*>(x), rows, cols, mode, scale_io, scale_given, q, ws, st);
+    }
+}
+
+template <typename T>
+static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, int format, float* gs_io,
+                                   int gs_given, uint8_t* q, uint8_t* sf, size_t sf_bytes, int sf_needs_clear,
+                                   const int* group_offsets, int num_groups, uint32_t* ws, cudaStream_t st) {
+    const size_t n = static_cast<size_t>(rows) * cols;
+    cudaError_t e;
+    if (sf_needs_clear && sf_bytes > 0) {
+        e = cudaMemsetAsync(sf, 0, sf_bytes, st);
+        if (e != cudaSuccess) return e;
+    }
+    if (format == DSL_FP4_NV && !gs_given) {
+        e = cudaMemsetAsync(ws, 0, 4, st);
+        if (e != cudaSuccess) return e;
+        amax_kernel<T><<<grid_for(n / 16, 256, 148 * 16), 256, 0, st>>>(x, n, ws);
+        nvfp4_global_scale_kernel<<<1, 1, 0, st>>>(ws, gs_io);
+    }
+    const long long chunks = rows * (cols / 16);
+    const long long grid = (chunks + 255) / 256;
+    if (grid > 0) {
+        if (format == DSL_FP4_NV)
+            quant_fp4_kernel<T, 0><<<static_cast<unsigned>(grid), 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, q, sf, group_offsets, num_groups);
+        else
+            quant_fp4_kernel<T, 1><<<static_cast<unsigned>(grid), 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, q, sf, group_offsets, num_groups);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quant_fp4(const void* x, int dtype, long long rows, long long cols, int format, float* gs_io,
+                             int gs_given, uint8_t* q, uint8_t* sf, size_t sf_bytes, int sf_needs_clear,
+                             const int* group_offsets, int num_groups, uint32_t* ws, cudaStream_t st) {
+    switch (dtype) {
+        case DSL_F32: return quant_fp4_typed(static_cast<const float*>(x), rows, cols, format, gs_io, gs_given, q, sf, sf_bytes, sf_needs_clear, group_offsets, num_groups, ws, st);
+        case DSL_BF16: return quant_fp4_typed(static_cast<const __nv_bfloat16*>(x), rows, cols, format, gs_io, gs_given, q, sf, sf_bytes, sf_needs_clear, group_offsets, num_groups, ws, st);
+        default: return quant_fp4_typed(static_cast<const __half*>(x), rows, cols, format, gs_io, gs_given, q, sf, sf_bytes, sf_needs_clear, group_offsets, num_groups, ws, st);
+    }
+}
+
+cudaError_t launch_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, cudaStream_t st) {
+    dim3 grid((C + 63) / 64, (R + 63) / 64);
+    if (grid.x > 0 && grid.y > 0) transpose_u8_kernel<<<grid, 256, 0, st>>>(in, out, R, C);
+    return cudaGetLastError();
+}
+
+}  // namespace dsl

@@ -1,0 +1,381 @@
+"""The "cuda" backend's GEMM callables: `fp8_gemm`, `fp4_gemm`, `grouped_gemm` (+ `bf16_gemm`).
+
+Drop-in for the callables the reference registers under the same kernel names
+(triton/gemm/gemm_kernels.py:104-122 `fp8_gemm`, :164-182 `grouped_gemm`;
+tilelang/gemm/gemm_kernels.py:96-133) and for the host wrapper `fp4_gemm` of
+cuda/gemm/fp4_gemm.cu:140-146, which the reference never registered.  Positional
+arguments and defaults follow the reference (A [M,K], B [K,N], fp32 result); everything
+else is an optional JSON-scalar keyword so it travels through `scalar_params`.
+
+All compute runs in libdslgemm.so (hand-written sm_100a kernels).  No CPU path exists.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+from .quantize import PackedWeight, pack_weight, quantize_fp4, quantize_fp8, transpose_bytes
+
+_FLOAT_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+_BYTE_DTYPES = (torch.uint8, torch.int8, torch.float8_e4m3fn)
+_OUT_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+
+Scalar = Union[None, float, torch.Tensor]
+
+
+def _out_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        name = str(name).replace("torch.", "")
+    try:
+        return _OUT_DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"out_dtype must be float32 or bfloat16, got {name!r}") from None
+
+
+def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
+              row_scale: Optional[torch.Tensor], col_scale: Optional[torch.Tensor], keep: list) -> _lib.Epilogue:
+    ep = _lib.Epilogue()
+    for name, s in (("a", scale_a), ("b", scale_b)):
+        host, devp = 1.0, None
+        if isinstance(s, torch.Tensor):
+            t = s.detach().to(device=dev, dtype=torch.float32).reshape(-1)
+            if t.numel() != 1:
+                raise ValueError(f"scale_{name} must be a scalar")
+            keep.append(t)
+            devp = t.data_ptr()
+        elif s is not None:
+            host = float(s)
+        setattr(ep, f"scale_{name}_host", host)
+        setattr(ep, f"scale_{name}_dev", devp)
+    for name, t in (("row_scale", row_scale), ("col_scale", col_scale)):
+        if t is not None:
+            t = t.detach().to(device=dev, dtype=torch.float32).contiguous()
+            keep.append(t)
+            setattr(ep, name, t.data_ptr())
+    ep.out_dtype = _lib.F32 if out == torch.float32 else _lib.BF16
+    return ep
+
+
+def _bytes2d(t: torch.Tensor) -> torch.Tensor:
+    t = t.contiguous()
+    return t.view(torch.uint8) if t.dtype != torch.uint8 else t
+
+
+def _offsets_arg(offsets: Optional[torch.Tensor], dev) -> Tuple[Optional[torch.Tensor], int]:
+    if offsets is None:
+        return None, 1
+    if offsets.dtype != torch.int32 or offsets.dim() != 1 or offsets.numel() < 2:
+        raise TypeError("expert_offsets must be a 1-D int32 tensor of length groups+1")
+    offsets = offsets.to(dev).contiguous()
+    groups = offsets.numel() - 1
+    if groups > _lib.MAX_GROUPS:
+        raise ValueError(f"at most {_lib.MAX_GROUPS} groups are supported, got {groups}")
+    return offsets, groups
+
+
+# --------------------------------------------------------------------------------------
+# low-level launches on already-quantised operands
+# --------------------------------------------------------------------------------------
+
+def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, scale_b: Scalar, *, n: int,
+                       out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
+                       row_scale=None, col_scale=None) -> torch.Tensor:
+    """C = (qa @ qb^T) * scale_a * scale_b on E4M3 bytes; qa [M, K], qb_nk [G*N, K]."""
+    dev = _lib.require_cuda(qa, qb_nk)
+    qa, qb_nk = _bytes2d(qa), _bytes2d(qb_nk)
+    M, K = qa.shape
+    offs, groups = _offsets_arg(expert_offsets, dev)
+    if qb_nk.shape != (groups * n, K):
+        raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major bytes, got {tuple(qb_nk.shape)}")
+    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    keep: list = []
+    ep = _epilogue(dev, scale_a, scale_b, out.dtype, row_scale, col_scale, keep)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_gemm_fp8(qa.data_ptr(), qb_nk.data_ptr(), out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+                                     groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_gemm_fp8")
+    return out
+
+
+def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor, *,
+                                 n: int, sb_block: bool, out_dtype=torch.float32,
+                                 expert_offsets: Optional[torch.Tensor] = None,
+                                 row_scale=None, col_scale=None) -> torch.Tensor:
+    """C = sum_g (qa_g @ qb_g^T) * sa[:, g] * sb[g]; sa [M, K/128]; sb [G, K/128, N] per-column
+    (sb_block False, the layout of cuda/gemm/fp8_gemm.cu:75) or [G, ceil(N/128), K/128] blocks."""
+    dev = _lib.require_cuda(qa, qb_nk, sa, sb)
+    qa, qb_nk = _bytes2d(qa), _bytes2d(qb_nk)
+    M, K = qa.shape
+    if K % 128 != 0:
+        raise ValueError(f"K must be a multiple of 128 for group-scaled FP8, got {K}")
+    offs, groups = _offsets_arg(expert_offsets, dev)
+    if qb_nk.shape != (groups * n, K):
+        raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major bytes, got {tuple(qb_nk.shape)}")
+    sa = sa.to(torch.float32).contiguous()
+    sb = sb.to(torch.float32).contiguous()
+    if sa.numel() != M * (K // 128):
+        raise ValueError(f"scale_a must have {M}x{K // 128} elements, got {tuple(sa.shape)}")
+    want_sb = groups * ((n + 127) // 128) * (K // 128) if sb_block else groups * (K // 128) * n
+    if sb.numel() != want_sb:
+        raise ValueError(f"scale_b must have {want_sb} elements, got {tuple(sb.shape)}")
+    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    keep: list = []
+    ep = _epilogue(dev, None, None, out.dtype, row_scale, col_scale, keep)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_gemm_fp8_groupwise(qa.data_ptr(), qb_nk.data_ptr(), sa.data_ptr(), sb.data_ptr(),
+                                               1 if sb_block else 0, out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+                                               groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(),
+                                               _lib.stream_ptr())
+    _lib.check(rc, "dsl_gemm_fp8_groupwise")
+    return out
+
+
+def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, *,
+                       format: str, n: int, global_scale_a: Scalar = None, global_scale_b: Scalar = None,
+                       out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
+                       row_scale=None, col_scale=None) -> torch.Tensor:
+    """Block-scaled FP4 GEMM on packed e2m1 operands pa [M, K/2], pb_nk [G*N, K/2] with tiled
+    scale bytes; for NVFP4 the result is multiplied once by global_scale_a * global_scale_b."""
+    dev = _lib.require_cuda(pa, pb_nk, sfa, sfb)
+    pa, pb_nk = _bytes2d(pa), _bytes2d(pb_nk)
+    M, kb2 = pa.shape
+    K = kb2 * 2
+    offs, groups = _offsets_arg(expert_offsets, dev)
+    if pb_nk.shape != (groups * n, kb2):
+        raise ValueError(f"weight must be [{groups}*{n}, {kb2}] packed bytes, got {tuple(pb_nk.shape)}")
+    fmt = {"nvfp4": _lib.FP4_NV, "mxfp4": _lib.FP4_MX}.get(format)
+    if fmt is None:
+        raise ValueError(f"format must be 'nvfp4' or 'mxfp4', got {format!r}")
+    nblk = K // 16 if format == "nvfp4" else K // 32
+    katoms = (nblk + 3) // 4
+    need_a = (((M + 127) // 128) if offs is None else 0) * katoms * 512
+    if sfa.numel() < need_a or sfb.numel() < groups * ((n + 127) // 128) * katoms * 512:
+        raise ValueError("scale buffers are smaller than the tiled layout needs")
+    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    keep: list = []
+    ep = _epilogue(dev, global_scale_a, global_scale_b, out.dtype, row_scale, col_scale, keep)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_gemm_fp4(pa.data_ptr(), pb_nk.data_ptr(), _bytes2d(sfa).data_ptr(),
+                                     _bytes2d(sfb).data_ptr(), fmt, out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+                                     groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_gemm_fp4")
+    return out
+
+
+def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torch.float32,
+                  expert_offsets: Optional[torch.Tensor] = None, scale_a: Scalar = None,
+                  scale_b: Scalar = None) -> torch.Tensor:
+    dev = _lib.require_cuda(a, b_nk)
+    a = a.to(torch.bfloat16).contiguous()
+    b_nk = b_nk.to(torch.bfloat16).contiguous()
+    M, K = a.shape
+    offs, groups = _offsets_arg(expert_offsets, dev)
+    if b_nk.shape != (groups * n, K):
+        raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major, got {tuple(b_nk.shape)}")
+    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    keep: list = []
+    ep = _epilogue(dev, scale_a, scale_b, out.dtype, None, None, keep)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_gemm_bf16(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+                                      groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_gemm_bf16")
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# quantise-and-multiply on one packed weight (shared by the public callables)
+# --------------------------------------------------------------------------------------
+
+def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
+           expert_offsets: Optional[torch.Tensor] = None, row_scale=None, col_scale=None) -> torch.Tensor:
+    """a [M, K] high-precision activations x packed weight -> [M, N]: quantise the activations
+    in the weight's format (one pass on the GPU) and run the matching GEMM."""
+    if a.dim() != 2 or a.shape[1] != w.k:
+        raise ValueError(f"activations must be [M, {w.k}], got {tuple(a.shape)}")
+    if w.groups > 1 and expert_offsets is None:
+        raise ValueError("a multi-group weight needs expert_offsets")
+    common = dict(n=w.n, out_dtype=out_dtype, expert_offsets=expert_offsets)
+    if w.format == "bf16":
+        return gemm_bf16_raw(a, w.q, **common)
+    if w.format == "fp8":
+        qa, sa = quantize_fp8(a, "per_tensor")
+        return gemm_fp8_quantized(qa, w.q, sa, w.scale, row_scale=row_scale, col_scale=col_scale, **common)
+    if w.format == "fp8_block128":
+        qa, sa = quantize_fp8(a, "groupwise")
+        return gemm_fp8_groupwise_quantized(qa, w.q, sa, w.scale, sb_block=True, row_scale=row_scale,
+                                            col_scale=col_scale, **common)
+    if w.format in ("nvfp4", "mxfp4"):
+        pa, sfa, gsa = quantize_fp4(a, w.format, group_offsets=expert_offsets)
+        return gemm_fp4_quantized(pa, w.q, sfa, w.scale, format=w.format, global_scale_a=gsa,
+                                  global_scale_b=w.global_scale, row_scale=row_scale, col_scale=col_scale, **common)
+    raise ValueError(f"unknown packed-weight format {w.format!r}")
+
+
+# --------------------------------------------------------------------------------------
+# public callables (the registry entries)
+# --------------------------------------------------------------------------------------
+
+def fp8_gemm(A: torch.Tensor, B, scale_a: Scalar = None, scale_b: Scalar = None, *, mode: str = "per_tensor",
+             group_size: int = 128, b_layout: str = "kn", out_dtype="float32",
+             row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """FP8 E4M3 GEMM, C[M,N] = A[M,K] @ B[K,N] (triton/gemm/gemm_kernels.py:104-122).
+
+    * A and B already E4M3 (float8_e4m3fn / uint8 / int8 bytes): `scale_a`, `scale_b` are the
+      dequantisation scales - floats for mode "per_tensor" (result (A@B)*scale_a*scale_b, fp32,
+      as the reference), or fp32 tensors for mode "groupwise" (scale_a [M, K/128], scale_b
+      [K/128, N], layout of cuda/gemm/fp8_gemm.cu:74-75) or "block128" (scale_b [N/128, K/128]).
+    * A and B high-precision (float32 / bfloat16 / float16): they are quantised on the GPU
+      first - per tensor with scale amax/448 (cuda/gemm/fp8_gemm.cu:119-144; a given scale_a /
+      scale_b is used instead of the amax-derived one), or, for "groupwise"/"block128", with
+      1x128 activation groups and 128x128 weight blocks.
+    b_layout "kn" is the reference's B[K,N]; "nk" is a K-major weight [N,K] (no transpose
+    needed).  B may also be a PackedWeight.
+    """
+    if mode not in ("per_tensor", "groupwise", "block128"):
+        raise ValueError(f"mode must be per_tensor, groupwise or block128, got {mode!r}")
+    if int(group_size) != 128 and mode != "per_tensor":
+        raise ValueError("only group_size=128 is supported")
+    if b_layout not in ("kn", "nk"):
+        raise ValueError("b_layout must be 'kn' or 'nk'")
+    dev = _lib.require_cuda(A, B if isinstance(B, torch.Tensor) else None)
+    if A.dim() != 2:
+        raise ValueError(f"A must be [M, K], got {tuple(A.shape)}")
+    M, K = A.shape
+    if isinstance(B, PackedWeight):
+        want = "fp8" if mode == "per_tensor" else "fp8_block128"
+        if B.format != want or B.groups != 1 or B.k != K:
+            raise ValueError(f"packed weight is {B.format} [{B.n},{B.k}], need {want} with K={K}")
+        return linear(A, B, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
+    if B.dim() != 2:
+        raise ValueError(f"B must be 2-D, got {tuple(B.shape)}")
+    if (B.shape[0] if b_layout == "kn" else B.shape[1]) != K:
+        raise ValueError(f"inner dimensions differ: A {tuple(A.shape)} vs B {tuple(B.shape)} ({b_layout})")
+    N = B.shape[1] if b_layout == "kn" else B.shape[0]
+    a_q, b_q = A.dtype in _BYTE_DTYPES, B.dtype in _BYTE_DTYPES
+    if a_q != b_q:
+        raise TypeError("A and B must both be E4M3 bytes or both be high-precision")
+    if a_q:
+        qb = _bytes2d(B)
+        if b_layout == "kn":
+            qb = transpose_bytes(qb)
+        if mode == "per_tensor":
+            if scale_a is None or scale_b is None:
+                raise ValueError("scale_a and scale_b are required for already-quantised operands")
+            return gemm_fp8_quantized(A, qb, scale_a, scale_b, n=N, out_dtype=out_dtype, row_scale=row_scale,
+                                      col_scale=col_scale)
+        if not isinstance(scale_a, torch.Tensor) or not isinstance(scale_b, torch.Tensor):
+            raise TypeError("group-scaled FP8 needs scale_a and scale_b tensors")
+        return gemm_fp8_groupwise_quantized(A, qb, scale_a, scale_b, n=N, sb_block=(mode == "block128"),
+                                            out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
+    if A.dtype not in _FLOAT_DTYPES or B.dtype not in _FLOAT_DTYPES:
+        raise TypeError(f"unsupported dtypes {A.dtype}, {B.dtype}")
+    Bnk = B.t().contiguous() if b_layout == "kn" else B.contiguous()
+    if mode == "per_tensor":
+        qa, sa = quantize_fp8(A, "per_tensor", scale=scale_a)
+        qb, sb = quantize_fp8(Bnk, "per_tensor", scale=scale_b)
+        return gemm_fp8_quantized(qa, qb, sa, sb, n=N, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
+    qa, sa = quantize_fp8(A, "groupwise")
+    qb, sb = quantize_fp8(Bnk, "block128")
+    return gemm_fp8_groupwise_quantized(qa, qb, sa, sb, n=N, sb_block=True, out_dtype=out_dtype,
+                                        row_scale=row_scale, col_scale=col_scale)
+
+
+def fp4_gemm(A: torch.Tensor, B, scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
+             use_mxfp4: bool = False, *, format: Optional[str] = None, b_layout: str = "kn",
+             global_scale_a: Scalar = None, global_scale_b: Scalar = None, out_dtype="float32",
+             row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Block-scaled FP4 GEMM; argument order of the reference host wrapper
+    `fp4_gemm(A, B, C, scale_a, scale_b, M, N, K, use_mxfp4)` (cuda/gemm/fp4_gemm.cu:140-146), with
+    M, N, K read from the tensors and C returned.
+
+    format "nvfp4" (default; e2m1 + unsigned-E4M3 scale per 16 + fp32 global scale) or "mxfp4"
+    (`use_mxfp4=True`; e2m1 + E8M0 scale per 32).
+    * High-precision A [M,K] and B ([K,N] for b_layout "kn", [N,K] for "nk"): quantised on the GPU.
+    * Packed operands (uint8/int8, two e2m1 per byte, low nibble first): A [M,K/2], B K-major
+      [N,K/2] (b_layout must be "nk"), `scale_a` / `scale_b` the tiled scale bytes, and for
+      NVFP4 `global_scale_a` / `global_scale_b`.
+    """
+    fmt = format if format is not None else ("mxfp4" if use_mxfp4 else "nvfp4")
+    if fmt not in ("nvfp4", "mxfp4"):
+        raise ValueError(f"format must be 'nvfp4' or 'mxfp4', got {fmt!r}")
+    if b_layout not in ("kn", "nk"):
+        raise ValueError("b_layout must be 'kn' or 'nk'")
+    _lib.require_cuda(A, B if isinstance(B, torch.Tensor) else None)
+    if A.dim() != 2:
+        raise ValueError(f"A must be 2-D, got {tuple(A.shape)}")
+    if isinstance(B, PackedWeight):
+        if B.format != fmt or B.groups != 1:
+            raise ValueError(f"packed weight is {B.format}, need single-group {fmt}")
+        return linear(A, B, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
+    if A.dtype in _BYTE_DTYPES:
+        if b_layout != "nk":
+            raise ValueError("packed FP4 weights must be K-major: pass b_layout='nk' with B [N, K/2]")
+        if scale_a is None or scale_b is None:
+            raise ValueError("packed operands need scale_a and scale_b (tiled scale bytes)")
+        return gemm_fp4_quantized(A, B, scale_a, scale_b, format=fmt, n=B.shape[0], global_scale_a=global_scale_a,
+                                  global_scale_b=global_scale_b, out_dtype=out_dtype, row_scale=row_scale,
+                                  col_scale=col_scale)
+    if A.dtype not in _FLOAT_DTYPES or B.dtype not in _FLOAT_DTYPES:
+        raise TypeError(f"unsupported dtypes {A.dtype}, {B.dtype}")
+    if (B.shape[0] if b_layout == "kn" else B.shape[1]) != A.shape[1]:
+        raise ValueError(f"inner dimensions differ: A {tuple(A.shape)} vs B {tuple(B.shape)} ({b_layout})")
+    w = pack_weight(B, fmt, layout=b_layout)
+    return linear(A, w, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
+
+
+def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_offsets: Optional[torch.Tensor] = None,
+                 *, format: str = "bf16", b_layout: str = "kn", out_dtype=None) -> torch.Tensor:
+    """Grouped GEMM for MoE / LoRA (triton/gemm/gemm_kernels.py:164-182, tilelang/gemm/gemm_kernels.py:116-133).
+
+    Fixed-size groups: A [G,M,K], B [G,K,N] -> [G,M,N] (the reference's form; `num_groups`
+    optional, checked against A when given).  Ragged groups (cuda/gemm/grouped_gemm.cu:79-104):
+    A [sum M_g, K] with `expert_offsets` int32 [G+1] on the device -> [sum M_g, N]; groups may
+    be empty and their sizes never leave the GPU.
+    format "bf16" multiplies unquantised (result in A.dtype, as the Triton reference); "fp8",
+    "fp8_groupwise", "nvfp4", "mxfp4" quantise A and B on the GPU first (result fp32 unless
+    out_dtype says otherwise).  B may be a PackedWeight.  b_layout "kn": B [G,K,N]; "nk": [G,N,K].
+    """
+    formats = {"bf16": "bf16", "fp8": "fp8", "fp8_groupwise": "fp8_block128", "nvfp4": "nvfp4", "mxfp4": "mxfp4"}
+    if format not in formats:
+        raise ValueError(f"format must be one of {sorted(formats)}, got {format!r}")
+    dev = _lib.require_cuda(A, B if isinstance(B, torch.Tensor) else None, expert_offsets)
+    fixed = A.dim() == 3
+    if not fixed and (A.dim() != 2 or expert_offsets is None):
+        raise ValueError("A must be [G,M,K], or [sum M, K] together with expert_offsets")
+    if isinstance(B, PackedWeight):
+        w = B
+        if w.format != formats[format]:
+            raise ValueError(f"packed weight is {w.format}, need {formats[format]}")
+    else:
+        if B.dim() != 3:
+            raise ValueError(f"B must be 3-D, got {tuple(B.shape)}")
+        w = pack_weight(B, formats[format], layout=b_layout)
+    G = w.groups
+    if num_groups is not None and int(num_groups) != G:
+        raise ValueError(f"num_groups={num_groups} but B holds {G} groups")
+    if fixed:
+        if A.shape[0] != G:
+            raise ValueError(f"A holds {A.shape[0]} groups but B holds {G}")
+        Mg = A.shape[1]
+        a2 = A.reshape(G * Mg, A.shape[2])
+        offs = torch.arange(G + 1, dtype=torch.int32, device=dev) * Mg
+    else:
+        a2 = A
+        offs = expert_offsets
+        if offs.numel() != G + 1:
+            raise ValueError(f"expert_offsets must have {G + 1} entries, got {offs.numel()}")
+    if out_dtype is None:
+        out_dtype = A.dtype if (format == "bf16" and A.dtype in (torch.float32, torch.bfloat16)) else torch.float32
+    if G == 1:
+        offs = None
+    out = linear(a2.contiguous(), w, out_dtype=out_dtype, expert_offsets=offs)
+    return out.reshape(G, Mg, w.n) if fixed else out
+
+
+def bf16_gemm(A: torch.Tensor, B: torch.Tensor, *, b_layout: str = "kn", out_dtype="float32") -> torch.Tensor:
+    """BF16 GEMM with fp32 accumulation, C = A[M,K] @ B[K,N] -> fp32 (triton/gemm/gemm_kernels.py:49-65)."""
+    w = pack_weight(B, "bf16", layout=b_layout)
+    return linear(A, w, out_dtype=out_dtype)

@@ -1,0 +1,147 @@
+/*
+ * libdslgemm - C ABI of the B200 (sm_100a) quantised-GEMM library.
+ *
+ * Every entry point takes raw device pointers and an explicit CUDA stream (passed as
+ * void*, i.e. a cudaStream_t), allocates nothing, never synchronises, and returns
+ *     0   success (work enqueued on the stream)
+ *   < 0   invalid argument (DSL_ERR_*), nothing enqueued
+ *   > 0   a cudaError_t value from the launch
+ * Kernels that wait on hardware barriers bound every wait; a kernel that gave up ORs a
+ * DSL_ST_* bit into the caller's status word (device memory, may be NULL) and exits
+ * cleanly, so the context stays usable.  Read the word after synchronising the stream.
+ *
+ * Operand conventions: A is [M, K] row-major (K contiguous); weights are K-major
+ * [N, K] (or [G, N, K] for grouped GEMM).  FP4 operands hold two e2m1 values per byte,
+ * low nibble = even k.  Block-scale bytes use the 512-byte tile layout
+ *   tile(rt, kt) at (rt * ceil(nblk/4) + kt) * 512,  byte(r, c) at (r%32)*16 + (r/32)*4 + c
+ * for 128 rows x 4 K-blocks per tile; dsl_sf_bytes() gives the buffer size.
+ */
+#ifndef DSLGEMM_H_
+#define DSLGEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { DSL_F32 = 0, DSL_BF16 = 1, DSL_F16 = 2 };                       /* input / output dtypes */
+enum { DSL_FP8_PER_TENSOR = 0, DSL_FP8_GROUP_1X128 = 1, DSL_FP8_BLOCK_128X128 = 2 };
+enum { DSL_FP4_NV = 0, DSL_FP4_MX = 1 };                                /* NVFP4 / MXFP4 */
+
+enum {
+    DSL_ERR_NULL = -1,        /* required pointer is NULL */
+    DSL_ERR_SHAPE = -2,       /* size negative, too large, or not a multiple the format needs */
+    DSL_ERR_ALIGN = -3,       /* pointer or leading dimension not 16-byte aligned */
+    DSL_ERR_ENUM = -4,        /* unknown dtype / mode / format */
+    DSL_ERR_DRIVER = -5,      /* the CUDA driver's tensor-map encoder is unavailable or refused */
+    DSL_ERR_TOO_LARGE = -6    /* beyond a stated fixed capacity */
+};
+enum {
+    DSL_ST_TIMEOUT_PRODUCER = 1, DSL_ST_TIMEOUT_MMA = 2, DSL_ST_TIMEOUT_EPILOGUE = 4, DSL_ST_TIMEOUT_TEST = 8
+};
+
+#define DSL_MAX_GROUPS 1024
+
+const char* dsl_version(void);
+
+/* Bytes of the tiled scale-factor buffer for `rows` x `nblk` scale bytes (one group). */
+size_t dsl_sf_bytes(long long rows, long long nblk);
+/* Same for ragged row groups, each padded to whole 128-row tiles: upper bound that needs
+ * no knowledge of the split - (ceil(rows/128) + groups) tiles. */
+size_t dsl_sf_bytes_grouped(long long rows, long long nblk, int groups);
+
+/*
+ * FP8 E4M3 quantisation.  Replaces quantize_to_fp8_kernel (cuda/gemm/fp8_gemm.cu:119-144)
+ * and extends it to 1x128 K-groups and 128x128 blocks.
+ *   x          [rows, cols] of `dtype`, contiguous, 16-byte aligned; cols % 16 == 0 for the grouped modes
+ *   scale_io   per-tensor: 1 float (written, or read when scale_given != 0)
+ *              1x128: [rows, ceil(cols/128)] written;  128x128: [ceil(rows/128), ceil(cols/128)] written
+ *   q_out      [rows, cols] bytes
+ *   ws         4 bytes of scratch (per-tensor amax)
+ */
+int dsl_quant_fp8(const void* x, int dtype, long long rows, long long cols, int mode, float* scale_io,
+                  int scale_given, uint8_t* q_out, void* ws, void* stream);
+
+/*
+ * FP4 e2m1 quantisation with block scales.  Replaces quantize_fp32_to_nvfp4
+ * (cuda/gemm/fp4_gemm.cu:50-90) for the two standard formats:
+ *   DSL_FP4_NV  one unsigned-E4M3 scale per 16 K-elements + fp32 global scale (cols % 32 == 0)
+ *   DSL_FP4_MX  one E8M0 scale per 32 K-elements                               (cols % 32 == 0)
+ *   gs_io      NVFP4 global scale: written (amax/2688), or read when gs_given != 0; unused for MX
+ *   q_out      [rows, cols/2] bytes;  sf_out tiled scale bytes (dsl_sf_bytes / _grouped)
+ *   group_offsets  NULL, or int32[groups+1] device array of row offsets (ragged expert
+ *              groups, each starting a fresh 128-row scale tile); groups <= DSL_MAX_GROUPS
+ *   ws         4 bytes of scratch
+ */
+int dsl_quant_fp4(const void* x, int dtype, long long rows, long long cols, int format, float* gs_io,
+                  int gs_given, uint8_t* q_out, uint8_t* sf_out, const int* group_offsets, int groups,
+                  void* ws, void* stream);
+
+/* Byte-matrix transpose [R, C] -> [C, R]: turns the reference's [K, N] weight layout
+ * (cuda/gemm/fp8_gemm.cu:29-35, B[k*N+n]) into the K-major [N, K] the tensor cores read. */
+int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream);
+
+/* Epilogue description shared by the GEMM entry points.
+ *   out = acc * scale_a * scale_b [* row_scale[m]] [* col_scale[g*N+n]]
+ * scale_x is *scale_x_dev when that pointer is non-NULL, else scale_x_host. */
+typedef struct {
+    float scale_a_host, scale_b_host;
+    const float* scale_a_dev;
+    const float* scale_b_dev;
+    const float* row_scale;     /* [M_total] or NULL: per-token rescale */
+    const float* col_scale;     /* [G, N]   or NULL: per-channel rescale */
+    int out_dtype;              /* DSL_F32 or DSL_BF16 */
+} dsl_epilogue;
+
+/*
+ * Dense / grouped FP8 E4M3 GEMM, per-tensor scales: C[m,n] = sum_k A[m,k] B[n,k] * scale_a * scale_b.
+ * Replaces fp8_gemm_per_tensor (cuda/gemm/fp8_gemm.cu:102-108) and the registered Triton
+ * fp8_gemm (triton/gemm/gemm_kernels.py:104-122).  K % 16 == 0.
+ * Grouped form (group_offsets != NULL): A is [M_total, K] with group g owning rows
+ * offsets[g]..offsets[g+1]; B is [G, N, K]; C is [M_total, N]
+ * (variable-size groups of cuda/gemm/grouped_gemm.cu:79-104, GemmProblem at :27-32).
+ */
+int dsl_gemm_fp8(const uint8_t* A, const uint8_t* B, void* C, long long ldc, long long M_total, int N, int K,
+                 const int* group_offsets, int groups, const dsl_epilogue* ep, uint32_t* status, void* stream);
+
+/*
+ * Dense / grouped BF16 GEMM, fp32 accumulate (same conventions as dsl_gemm_fp8, operands bf16).
+ * Replaces the registered grouped_gemm (triton/gemm/gemm_kernels.py:164-182; fixed-size groups of
+ * cuda/gemm/grouped_gemm.cu:36-75 when all groups have equal rows) for unquantised inputs.  K % 8 == 0.
+ */
+int dsl_gemm_bf16(const void* A, const void* B, void* C, long long ldc, long long M_total, int N, int K,
+                  const int* group_offsets, int groups, const dsl_epilogue* ep, uint32_t* status, void* stream);
+
+/*
+ * FP8 GEMM with fp32 group scales along K (G = 128):
+ *   C[m,n] = sum_g (sum_{k in g} A[m,k] B[n,k]) * sa[m,g] * sb[g,n]
+ * Replaces fp8_gemm_groupwise (cuda/gemm/fp8_gemm.cu:69-99,110-116).  sa is [M_total, K/128];
+ * sb is [G, K/128, N] per-column scales when sb_block == 0 (the reference layout), or
+ * [G, ceil(N/128), K/128] 128x128 block scales when sb_block != 0.  K % 128 == 0.
+ */
+int dsl_gemm_fp8_groupwise(const uint8_t* A, const uint8_t* B, const float* sa, const float* sb, int sb_block,
+                           void* C, long long ldc, long long M_total, int N, int K, const int* group_offsets,
+                           int groups, const dsl_epilogue* ep, uint32_t* status, void* stream);
+
+/*
+ * Dense / grouped block-scaled FP4 GEMM on packed e2m1 operands.
+ * Replaces fp4_gemm (cuda/gemm/fp4_gemm.cu:95-146) for the two standard formats; for NVFP4 the
+ * epilogue's scale_a/scale_b carry the two global scales.  sfa / sfb are tiled scale bytes
+ * (sfa over A's rows - with ragged groups each group starts a fresh tile; sfb over [G][N]
+ * with ceil(N/128) tiles per group).  K % 32 == 0.
+ */
+int dsl_gemm_fp4(const uint8_t* A, const uint8_t* B, const uint8_t* sfa, const uint8_t* sfb, int format, void* C,
+                 long long ldc, long long M_total, int N, int K, const int* group_offsets, int groups,
+                 const dsl_epilogue* ep, uint32_t* status, void* stream);
+
+/* Runs one bounded wait on a barrier nothing ever signals and reports DSL_ST_TIMEOUT_TEST
+ * in *status after about `limit_us` microseconds: exercises the give-up path without
+ * faulting or hanging the device. */
+int dsl_selftest_bounded_wait(uint32_t* status, unsigned limit_us, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSLGEMM_H_ */
