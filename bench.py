@@ -1,0 +1,366 @@
+"""Benchmark of the quantised-GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" = one pass of the hot path over one batch of synthetic input: quantise / scale-pack
+the activations (one kernel) and run the GEMM against weights that were quantised once.  The
+default workload is the FP8 groupwise GEMM at the Llama-3-8B MLP shape (M=4096, K=4096,
+N=14336; 1x128 activation scales, 128x128 weight-block scales, bf16 output).  Inputs are
+seeded synthetic tensors of the stated shapes and distributions.
+
+Prints ONE JSON line (rank 0).  `value` is aggregate TFLOP/s over all ranks with inputs
+resident in HBM; `e2e` is the same metric through the public callable with activations in
+pinned host memory (host->device copy of the activations and device->host copy of the result
+inside the timed region).  With N > 1 each rank holds its own column shard of the weight
+(dense) or its own experts (MoE) of the same per-rank size, no data-path collective.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, M, K, N, act std/outliers, weight std, description)
+    "fp8_groupwise_llama8b_mlp": dict(kind="fp8_block128", M=4096, K=4096, N=14336, wstd=0.02, outliers=False),
+    "fp8_per_tensor_1024": dict(kind="fp8", M=1024, K=1024, N=1024, wstd=1.0, outliers=False),
+    "fp8_groupwise_8192": dict(kind="fp8_block128", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
+    "nvfp4_8192": dict(kind="nvfp4", M=8192, K=8192, N=8192, wstd=0.02, outliers=True),
+    "nvfp4_m1024": dict(kind="nvfp4", M=1024, K=8192, N=8192, wstd=0.02, outliers=True),
+    "nvfp4_m128": dict(kind="nvfp4", M=128, K=8192, N=8192, wstd=0.02, outliers=True),
+    "nvfp4_m16": dict(kind="nvfp4", M=16, K=8192, N=8192, wstd=0.02, outliers=True),
+    "nvfp4_m1": dict(kind="nvfp4", M=1, K=8192, N=8192, wstd=0.02, outliers=True),
+    "mxfp4_llama70b_up": dict(kind="mxfp4", M=8192, K=8192, N=28672, wstd=0.015, outliers=False),
+    "mxfp4_llama70b_down": dict(kind="mxfp4", M=8192, K=28672, N=8192, wstd=0.015, outliers=False),
+    "moe_nvfp4": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
+    "moe_fp8_groupwise": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
+    "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
+}
+DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
+PEAK_MULT = {"fp8": 2.0, "fp8_block128": 2.0, "nvfp4": 4.0, "mxfp4": 4.0, "bf16": 1.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["bf16_tflops"], p["hbm_gbs"], "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def make_moe_offsets(rng, tokens, experts, topk):
+    logits = rng.standard_normal((tokens, experts)).astype(np.float32)
+    top = np.argpartition(-logits, topk - 1, axis=1)[:, :topk]
+    counts = np.bincount(top.reshape(-1), minlength=experts)
+    return np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+
+
+def build_workload(name, rank, world, device, sets):
+    """Returns dict(step=callable(i)->out, gemm=callable, flops, rows, desc...) with `sets`
+    rotating copies of inputs so consecutive steps never reuse L2-resident operands."""
+    from dsl_tool_b200 import pack_weight
+    from dsl_tool_b200.gemm_kernels import linear
+    cfg = WORKLOADS[name]
+    kind = cfg["kind"]
+    g = torch.Generator(device=device).manual_seed(1234 + rank)
+    offs = None
+    if cfg.get("moe"):
+        experts = cfg["experts"]          # per rank: weak scaling keeps 64 local experts per GPU
+        offs_np = make_moe_offsets(np.random.default_rng(99 + rank), cfg["tokens"], experts, cfg["topk"])
+        offs = torch.from_numpy(offs_np).to(device)
+        M, K, N = int(offs_np[-1]), cfg["K"], cfg["N"]
+        wshape = (experts, N, K)
+    else:
+        M, K, N = cfg["M"], cfg["K"], cfg["N"]
+        wshape = (1, N, K)
+    acts, wts = [], []
+    for s in range(sets):
+        a = torch.randn((M, K), generator=g, device=device, dtype=torch.float32)
+        if cfg.get("outliers"):
+            mask = torch.rand((M, K), generator=g, device=device) < 1e-3
+            sign = torch.where(torch.rand((M, K), generator=g, device=device) < 0.5, -20.0, 20.0)
+            a = torch.where(mask, sign, a)
+        acts.append(a.to(torch.bfloat16))
+        del a
+        w = (torch.randn(wshape, generator=g, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
+        wts.append(pack_weight(w, kind, layout="nk"))
+        del w
+    torch.cuda.synchronize()
+
+    def step(i, a=None):
+        return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype=torch.bfloat16, expert_offsets=offs)
+
+    return dict(step=step, acts=acts, wts=wts, offs=offs, M=M, K=K, N=N, kind=kind, flops=2.0 * M * N * K,
+                moe=bool(cfg.get("moe")))
+
+
+def split_step(wl):
+    """(quantise, gemm) closures so the GEMM launch can be bracketed by its own events."""
+    from dsl_tool_b200 import quantize_fp4, quantize_fp8
+    from dsl_tool_b200 import gemm_kernels as GK
+    kind, offs, sets = wl["kind"], wl["offs"], len(wl["acts"])
+
+    def quant(i):
+        a = wl["acts"][i % sets]
+        if kind == "fp8":
+            return quantize_fp8(a, "per_tensor")
+        if kind == "fp8_block128":
+            return quantize_fp8(a, "groupwise")
+        if kind in ("nvfp4", "mxfp4"):
+            return quantize_fp4(a, kind, group_offsets=offs)
+        return (a,)
+
+    def gemm(i, q):
+        w = wl["wts"][i % sets]
+        common = dict(n=w.n, out_dtype=torch.bfloat16, expert_offsets=offs)
+        if kind == "fp8":
+            return GK.gemm_fp8_quantized(q[0], w.q, q[1], w.scale, **common)
+        if kind == "fp8_block128":
+            return GK.gemm_fp8_groupwise_quantized(q[0], w.q, q[1], w.scale, sb_block=True, **common)
+        if kind in ("nvfp4", "mxfp4"):
+            return GK.gemm_fp4_quantized(q[0], w.q, q[1], w.scale, format=kind, global_scale_a=q[2],
+                                         global_scale_b=w.global_scale, **common)
+        return GK.gemm_bf16_raw(q[0], w.q, **common)
+
+    return quant, gemm
+
+
+def cpu_baseline(name, sample_rows, steps=1, warmup=0):
+    """The oracle's fp32-accumulated dequantised GEMM (numpy, all host threads) on the first
+    `sample_rows` activation rows of the workload, full N and K.  Returns (TFLOP/s, cores, text)."""
+    from oracle import quant_oracle as O
+    cfg = WORKLOADS[name]
+    kind = cfg["kind"]
+    rng = np.random.default_rng(5)
+    K, N = cfg["K"], cfg["N"]
+    R = sample_rows
+    a = rng.standard_normal((R, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * cfg["wstd"]).astype(np.float32)
+    if kind == "fp8_block128":
+        qa, sa = O.quant_fp8_groupwise(a)
+        qb, sbb = O.quant_fp8_block(w)
+        sb = O.expand_block_scale(sbb, N)
+        fn = lambda: O.gemm_fp8_groupwise(qa, qb, sa, sb)
+    elif kind == "fp8":
+        qa, sa = O.quant_fp8_per_tensor(a)
+        qb, sb = O.quant_fp8_per_tensor(w)
+        fn = lambda: O.gemm_fp8_per_tensor(qa, qb, sa, sb)
+    elif kind == "nvfp4":
+        pa, sfa, gsa = O.quant_nvfp4(a)
+        pb, sfb, gsb = O.quant_nvfp4(w)
+        fn = lambda: O.gemm_nvfp4(pa, sfa, gsa, pb, sfb, gsb)
+    elif kind == "mxfp4":
+        pa, sfa = O.quant_mxfp4(a)
+        pb, sfb = O.quant_mxfp4(w)
+        fn = lambda: O.gemm_mxfp4(pa, sfa, pb, sfb)
+    else:
+        fn = lambda: a @ w.T
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    cores = os.cpu_count() or 1
+    return 2.0 * R * N * K / dt / 1e12, cores, dt, f"first {R} activation rows x full N={N}, K={K} (dequantise + fp32 GEMM per step)"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = WORKLOADS[args.workload]
+    rows = 512 if not cfg.get("moe") else 512
+    val, cores, dt, sample = cpu_baseline(args.workload, rows, steps=args.steps, warmup=min(args.warmup, 2))
+    line = {
+        "impl": "reference", "metric": "gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_NAME[cfg["kind"]], "data": "synthetic",
+        "config": {"workload": args.workload, "note": "CPU port of the reference emulation (oracle), bounded sample"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="fp8_groupwise_llama8b_mlp", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sets", type=int, default=4, help="rotating input sets (keeps operands out of L2)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    from dsl_tool_b200 import _lib
+    wl = build_workload(args.workload, rank, world, device, args.sets)
+    quant, gemm = split_step(wl)
+    K_steps, W = args.steps, args.warmup
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------------------
+    for i in range(W):
+        gemm(i, quant(i))
+    _lib.check_status(device)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K_steps)]
+    barrier()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(K_steps):
+        ev[i][0].record()
+        q = quant(i)
+        ev[i][1].record()
+        out = gemm(i, q)
+        ev[i][2].record()
+    t_end.record()
+    barrier()
+    total_ms = t_start.elapsed_time(t_end)
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status(device)
+    gemm_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    quant_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+
+    # ---- end to end: activations from pinned host memory, result back to the host -----------
+    host_a = [torch.empty_like(a, device="cpu").pin_memory() for a in wl["acts"][:2]]
+    for h, a in zip(host_a, wl["acts"]):
+        h.copy_(a)
+    dev_a = torch.empty_like(wl["acts"][0])
+    host_out = torch.empty((wl["M"], wl["N"]), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(K_steps, 10))
+    for i in range(2):
+        dev_a.copy_(host_a[i % 2], non_blocking=True)
+        host_out.copy_(wl["step"](i, dev_a), non_blocking=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(e2e_steps):
+        dev_a.copy_(host_a[i % 2], non_blocking=True)
+        host_out.copy_(wl["step"](i, dev_a), non_blocking=True)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- aggregate over ranks (max time, summed work) ------------------------------------------
+    stats = torch.tensor([total_ms, e2e_ms, wl["flops"], gemm_ms, quant_ms], dtype=torch.float64, device=device)
+    if dist is not None:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, gemm_ms, quant_ms = mx[0].item(), mx[1].item(), mx[3].item(), mx[4].item()
+        flops_all = sm[2].item()
+    else:
+        flops_all = wl["flops"]
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = total_ms / K_steps
+    value = flops_all / (ms_per_step * 1e-3) / 1e12
+    bf16_peak, hbm_peak, basis = measured_peaks()
+    kind = wl["kind"]
+    achieved = wl["flops"] / (gemm_ms * 1e-3) / 1e12
+    peak = bf16_peak * PEAK_MULT[kind]
+    line = {
+        "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE_NAME[kind], "data": "synthetic",
+        "config": {"workload": args.workload, "M": wl["M"], "K": wl["K"], "N": wl["N"], "out": "bf16",
+                   "moe": wl["moe"], "per_rank": "own weight shard / experts of this size, no collective",
+                   "step": "activation quantise + GEMM, weights quantised once",
+                   "l2": f"inputs rotate over {args.sets} sets (larger than the 126 MB L2)"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": None,
+                     "kernel": "gemm", "kernel_ms": gemm_ms, "quant_kernel_ms": quant_ms,
+                     "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"},
+        "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": wl["M"] * wl["N"] * 2,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": 2 * K_steps if kind != "bf16" else K_steps,
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        rows = 512
+        val, cores, dt, sample = cpu_baseline(args.workload, rows)
+        line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
+                                "seconds": dt}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,74 @@
+"""The C-ABI library loads and exports every symbol include/dslgemm.h declares; argument
+validation that needs no GPU.  CPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from dsl_tool_b200 import _lib
+from dsl_tool_b200.build import build_library
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def cdll():
+    build_library()
+    return _lib.lib()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "dslgemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dsl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(cdll):
+    names = declared_functions()
+    assert len(names) >= 11
+    for n in names:
+        assert hasattr(cdll, n), n
+    assert set(names) == set(_lib._SIGNATURES)        # the Python binding covers the whole header
+
+
+def test_version_and_sizes(cdll):
+    assert b"sm_100a" in cdll.dsl_version()
+    assert cdll.dsl_sf_bytes(1, 1) == 512
+    assert cdll.dsl_sf_bytes(128, 4) == 512
+    assert cdll.dsl_sf_bytes(129, 5) == 4 * 512
+    assert cdll.dsl_sf_bytes(8192, 512) == 64 * 128 * 512
+    assert cdll.dsl_sf_bytes_grouped(300, 8, 4) == (3 + 4) * 2 * 512
+    assert cdll.dsl_sf_bytes(0, 4) == 0
+
+
+def test_argument_validation_without_gpu(cdll):
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf) & ~15
+    ep = _lib.Epilogue()
+    assert cdll.dsl_quant_fp8(None, 0, 4, 16, 0, p, 0, p, p, None) == -1          # NULL input
+    assert cdll.dsl_quant_fp8(p, 7, 4, 16, 0, p, 0, p, p, None) == -4             # bad dtype
+    assert cdll.dsl_quant_fp8(p, 0, 4, 24, 1, p, 0, p, p, None) == -2             # cols % 16 for grouped modes
+    assert cdll.dsl_quant_fp8(p + 4, 0, 4, 16, 0, p, 0, p, p, None) == -3         # misaligned
+    assert cdll.dsl_quant_fp4(p, 0, 4, 48, 0, p, 0, p, p, None, 0, p, None) == -2 # K % 32
+    assert cdll.dsl_quant_fp4(p, 0, 4, 64, 5, p, 0, p, p, None, 0, p, None) == -4
+    assert cdll.dsl_quant_fp4(p, 0, 4, 64, 0, p, 0, p, p, p, 5000, p, None) == -6 # too many groups
+    assert cdll.dsl_gemm_fp8(p, p, p, 16, 4, 16, 24, None, 1, ctypes.byref(ep), None, None) == -2   # K % 16
+    assert cdll.dsl_gemm_fp8(p, p, p, 8, 4, 16, 32, None, 1, ctypes.byref(ep), None, None) == -2    # ldc < N
+    assert cdll.dsl_gemm_fp8(p, p, p, 16, 4, 16, 32, None, 1, None, None, None) == -1
+    assert cdll.dsl_gemm_fp4(p, p, p, p, 0, p, 16, 4, 16, 48, None, 1, ctypes.byref(ep), None, None) == -2
+    assert cdll.dsl_gemm_fp4(p, p, None, p, 0, p, 16, 4, 16, 64, None, 1, ctypes.byref(ep), None, None) == -1
+    assert cdll.dsl_gemm_fp8_groupwise(p, p, p, p, 1, p, 16, 4, 16, 192, None, 1, ctypes.byref(ep), None, None) == -2
+    ep.out_dtype = 9
+    assert cdll.dsl_gemm_bf16(p, p, p, 16, 4, 16, 32, None, 1, ctypes.byref(ep), None, None) == -4
+    # empty problems are a no-op, not an error
+    ep.out_dtype = 0
+    assert cdll.dsl_gemm_fp8(p, p, p, 16, 0, 16, 32, None, 1, ctypes.byref(ep), None, None) == 0
+    assert cdll.dsl_quant_fp8(p, 0, 0, 16, 0, p, 0, p, p, None) == 0
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libdslgemm.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.lib()
