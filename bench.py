@@ -34,6 +34,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # name: (kind, M, K, N, act std/outliers, weight std, description)
     "fp8_groupwise_llama8b_mlp": dict(kind="fp8_block128", M=4096, K=4096, N=14336, wstd=0.02, outliers=False),
+    "fp8_groupwise_m1024": dict(kind="fp8_block128", M=1024, K=4096, N=14336, wstd=0.02, outliers=False),
     "fp8_per_tensor_1024": dict(kind="fp8", M=1024, K=1024, N=1024, wstd=1.0, outliers=False),
     "fp8_groupwise_8192": dict(kind="fp8_block128", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
     "nvfp4_8192": dict(kind="nvfp4", M=8192, K=8192, N=8192, wstd=0.02, outliers=True),
@@ -70,7 +71,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -231,7 +232,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="fp8_groupwise_llama8b_mlp", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -293,9 +294,9 @@ def main():
     quant_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
 
     # ---- end to end: activations from pinned host memory, result back to the host -----------
-    host_a = [torch.empty_like(a, device="cpu").pin_memory() for a in wl["acts"][:2]]
-    for h, a in zip(host_a, wl["acts"]):
-        h.copy_(a)
+    host_a = [torch.empty_like(wl["acts"][0], device="cpu").pin_memory() for _ in range(2)]
+    for j, h in enumerate(host_a):
+        h.copy_(wl["acts"][j % len(wl["acts"])])
     dev_a = torch.empty_like(wl["acts"][0])
     host_out = torch.empty((wl["M"], wl["N"]), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(K_steps, 10))
