@@ -17,6 +17,8 @@
 // linear tile index into (row group, row tile, column tile) from the group offsets, so ragged
 // expert groups need no host-side knowledge of their sizes.  Every barrier wait is bounded.
 #include <cuda_bf16.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "gemm.cuh"
 #include "gemm_tiles.cuh"
@@ -378,8 +380,22 @@ static int launch_one(const void* A, const void* B, const GemmArgs& args, long l
     return static_cast<int>(cudaGetLastError());
 }
 
+// Which kernel serves a problem: the CTA-pair kernel (256x256 tiles) once there is more than
+// one 128-row tile of work and the output is at least 256 wide; the 1-CTA kernel otherwise.
+// DSLGEMM_KERNEL=1cta|pair overrides the choice (for measurements).
+static int forced_kernel() {
+    static int v = []() {
+        const char* e = getenv("DSLGEMM_KERNEL");
+        if (e == nullptr) return 0;
+        return strcmp(e, "1cta") == 0 ? 1 : (strcmp(e, "pair") == 0 ? 2 : 0);
+    }();
+    return v;
+}
+
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st) {
     if (args.m_total <= 0 || args.n <= 0) return 0;
+    const int forced = forced_kernel();
+    if (forced == 2 || (forced == 0 && args.m_total > 128 && args.n >= 256)) return launch_gemm_pair(kind, A, B, args, st);
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
     // Narrow outputs get 128-wide tiles (two accumulator stages, more CTAs in flight).
     const bool narrow = args.n <= 128 || (args.n % 256 != 0 && args.n % 256 <= 128 && args.n < 1024);

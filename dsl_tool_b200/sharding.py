@@ -1,0 +1,158 @@
+"""Single-box partitioning of the quantised GEMMs: column-parallel weights for the dense
+GEMMs and expert-parallel weights for grouped GEMM, one process per GPU.
+
+The reference has no multi-device code at all (its dispatcher reports a single device,
+dispatcher/dispatcher.py:338-344); this module is the layer above `linear` that the north-star
+configs ask for.  The GEMM step itself needs no collective: output columns / experts are
+independent, so every rank runs the ordinary kernels on its shard.  Only when the caller wants
+the full output on every rank is an NCCL all-gather issued (over NVLink / NVSwitch), on the
+stream the GEMM ran on.
+
+Host logic (partition arithmetic, gather layout) is kept free of CUDA so it can be exercised
+with the gloo backend on CPU; the compute callable is injected (`linear_fn`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+COLUMN_ALIGN = 128   # scale-factor tiles and 128x128 weight blocks must stay whole inside a shard
+
+
+def column_ranges(n: int, world: int, align: int = COLUMN_ALIGN) -> List[Tuple[int, int]]:
+    """Contiguous column ranges [start, end) per rank, every boundary a multiple of `align`
+    (except the end of the matrix); ranks differ by at most one aligned block."""
+    if n <= 0 or world <= 0:
+        raise ValueError("n and world must be positive")
+    blocks = (n + align - 1) // align
+    base, extra = divmod(blocks, world)
+    out, start = [], 0
+    for r in range(world):
+        nb = base + (1 if r < extra else 0)
+        end = min(n, start + nb * align)
+        out.append((start, end))
+        start = end
+    return out
+
+
+def expert_ranges(groups: int, world: int) -> List[Tuple[int, int]]:
+    """Contiguous expert ranges [first, last) per rank, sizes differing by at most one."""
+    if groups < 0 or world <= 0:
+        raise ValueError("bad arguments")
+    base, extra = divmod(groups, world)
+    out, start = [], 0
+    for r in range(world):
+        n = base + (1 if r < extra else 0)
+        out.append((start, start + n))
+        start += n
+    return out
+
+
+def local_rows(expert_offsets: Sequence[int], first: int, last: int) -> Tuple[int, int, List[int]]:
+    """Rows of the expert-sorted activation matrix that belong to experts [first, last):
+    (row_start, row_end, local offsets rebased to 0)."""
+    r0, r1 = int(expert_offsets[first]), int(expert_offsets[last])
+    return r0, r1, [int(expert_offsets[g]) - r0 for g in range(first, last + 1)]
+
+
+def _world(group) -> Tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+@dataclass
+class ColumnParallelLinear:
+    """y[:, shard] = linear(x, W[shard, :]) on every rank; `gather=True` returns the full y.
+
+    `weight_shard` is whatever `linear_fn` accepts as its second argument (a PackedWeight for
+    the CUDA path); `n_total` is the unsharded output width.
+    """
+    weight_shard: object
+    n_total: int
+    linear_fn: Callable[..., torch.Tensor]
+    group: Optional[object] = None
+
+    def __post_init__(self):
+        self.rank, self.world = _world(self.group)
+        self.ranges = column_ranges(self.n_total, self.world)
+        self.start, self.end = self.ranges[self.rank]
+
+    def forward(self, x: torch.Tensor, gather: bool = False, **kw) -> torch.Tensor:
+        y = self.linear_fn(x, self.weight_shard, **kw)
+        if y.shape[1] != self.end - self.start:
+            raise ValueError(f"shard produced {y.shape[1]} columns, expected {self.end - self.start}")
+        if not gather or self.world == 1:
+            return y
+        return all_gather_columns(y, self.ranges, self.group)
+
+
+def all_gather_columns(y: torch.Tensor, ranges: Sequence[Tuple[int, int]], group=None) -> torch.Tensor:
+    """All-gather column shards [M, n_r] into [M, sum n_r] on every rank."""
+    world = len(ranges)
+    widths = [e - s for s, e in ranges]
+    m = y.shape[0]
+    y = y.contiguous()
+    if len(set(widths)) == 1:
+        buf = torch.empty((world * m, widths[0]), dtype=y.dtype, device=y.device)
+        dist.all_gather_into_tensor(buf, y, group=group)
+        return buf.view(world, m, widths[0]).permute(1, 0, 2).reshape(m, world * widths[0])
+    # uneven shards: pad to the widest, gather once, drop the padding
+    wmax = max(widths)
+    padded = y if y.shape[1] == wmax else torch.nn.functional.pad(y, (0, wmax - y.shape[1]))
+    buf = torch.empty((world * m, wmax), dtype=y.dtype, device=y.device)
+    dist.all_gather_into_tensor(buf, padded.contiguous(), group=group)
+    buf = buf.view(world, m, wmax)
+    return torch.cat([buf[r, :, :w] for r, w in enumerate(widths)], dim=1)
+
+
+@dataclass
+class ExpertParallelGroupedLinear:
+    """Grouped GEMM with the experts split across ranks: rank r owns experts
+    `expert_ranges(G, world)[r]` and multiplies only the rows routed to them.
+
+    `forward` takes the rows of this rank's experts (already expert-sorted) with their local
+    offsets.  `forward_from_global` slices them out of a replicated expert-sorted matrix and,
+    with `gather=True`, all-gathers the ragged row blocks back into the global order.
+    """
+    weight_local: object
+    groups_total: int
+    linear_fn: Callable[..., torch.Tensor]
+    group: Optional[object] = None
+
+    def __post_init__(self):
+        self.rank, self.world = _world(self.group)
+        self.ranges = expert_ranges(self.groups_total, self.world)
+        self.first, self.last = self.ranges[self.rank]
+
+    def forward(self, x_local: torch.Tensor, local_offsets: torch.Tensor, **kw) -> torch.Tensor:
+        return self.linear_fn(x_local, self.weight_local, expert_offsets=local_offsets, **kw)
+
+    def forward_from_global(self, x_sorted: torch.Tensor, expert_offsets: Sequence[int], gather: bool = False,
+                            **kw) -> torch.Tensor:
+        r0, r1, offs = local_rows(expert_offsets, self.first, self.last)
+        local = torch.tensor(offs, dtype=torch.int32, device=x_sorted.device)
+        y = self.forward(x_sorted[r0:r1], local, **kw)
+        if not gather or self.world == 1:
+            return y
+        rows = [int(expert_offsets[l]) - int(expert_offsets[f]) for f, l in self.ranges]
+        rmax = max(rows)
+        padded = y if y.shape[0] == rmax else torch.nn.functional.pad(y, (0, 0, 0, rmax - y.shape[0]))
+        buf = torch.empty((self.world * rmax, y.shape[1]), dtype=y.dtype, device=y.device)
+        dist.all_gather_into_tensor(buf, padded.contiguous(), group=self.group)
+        buf = buf.view(self.world, rmax, y.shape[1])
+        return torch.cat([buf[r, :n] for r, n in enumerate(rows)], dim=0)
+
+
+def shard_weight_columns(w_nk: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rows [start, end) of a K-major weight [N, K] for `rank` (a view)."""
+    s, e = column_ranges(w_nk.shape[0], world)[rank]
+    return w_nk[s:e]
+
+
+def shard_weight_experts(w_gnk: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    f, l = expert_ranges(w_gnk.shape[0], world)[rank]
+    return w_gnk[f:l]
