@@ -42,6 +42,8 @@ class Epilogue(ctypes.Structure):
         ("row_scale", ctypes.c_void_p),
         ("col_scale", ctypes.c_void_p),
         ("out_dtype", ctypes.c_int),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t),
     ]
 
 
@@ -144,6 +146,22 @@ def scratch_word(device: torch.device) -> torch.Tensor:
     if t is None:
         t = torch.zeros(4, dtype=torch.int32, device=device)
         _scratch[idx] = t
+    return t
+
+
+_workspace: Dict[tuple, torch.Tensor] = {}
+WORKSPACE_BYTES = 16 << 20
+
+
+def workspace(device: torch.device) -> torch.Tensor:
+    """Split-K scratch, one buffer per (device, stream): launches on one stream use it in
+    order, launches on different streams never share it."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    t = _workspace.get(key)
+    if t is None:
+        t = torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _workspace[key] = t
     return t
 
 

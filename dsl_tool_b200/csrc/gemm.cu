@@ -21,6 +21,7 @@
 #include <string.h>
 
 #include "gemm.cuh"
+#include "gemm_epilogue.cuh"
 #include "gemm_tiles.cuh"
 #include "ptx.cuh"
 
@@ -117,6 +118,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tw.block_n = BLOCK_N;
     tw.total = static_cast<long long>(tw.m_tiles) * tw.n_tiles;
     const int num_kb = (args.k_bytes + STAGE_KB - 1) / STAGE_KB;
+    // split-K: work item t = tile * split_k + slice; slice ks covers K-stages [ks*kb_per, ...)
+    const int split_k = args.split_k > 1 ? args.split_k : 1;
+    const int kb_per = (num_kb + split_k - 1) / split_k;
+    const long long total_items = tw.total * split_k;
 
     if (warp == 0) {
         // ================= TMA producer =================
@@ -124,9 +129,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long t = blockIdx.x; t < tw.total && ok; t += gridDim.x) {
-                const TileInfo ti = tw.decode(t);
-                for (int kb = 0; kb < num_kb; ++kb) {
+            for (long long t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+                const TileInfo ti = tw.decode(t / split_k);
+                const int kb0 = static_cast<int>(t % split_k) * kb_per;
+                const int kb1 = min(num_kb, kb0 + kb_per);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     uint32_t bytes = C::A_STAGE + C::B_STAGE;
                     int atoms = 0;
@@ -160,7 +167,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        if (lane == 0) {
+        {   // the warp stays converged; one elected lane issues (keeps operands warp-uniform)
             // instruction descriptor: M = 128, N = BLOCK_N, both operands K-major
             uint32_t idesc = (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
             if (KIND == KIND_F8) idesc |= 1u << 4;                                  // fp32 accumulate, E4M3 x E4M3
@@ -171,17 +178,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t phase = 0;
             bool ok = true;
             long long iter = 0;
-            for (long long t = blockIdx.x; t < tw.total && ok; t += gridDim.x, ++iter) {
+            for (long long t = blockIdx.x; t < total_items && ok; t += gridDim.x, ++iter) {
+                const int kb0 = static_cast<int>(t % split_k) * kb_per;
+                const int kb1 = min(num_kb, kb0 + kb_per);
                 const int acc = static_cast<int>(iter % C::ACC_STAGES);
                 const uint32_t acc_phase = static_cast<uint32_t>((iter / C::ACC_STAGES) & 1);
                 if (!mbar_wait(acc_empty + acc, acc_phase ^ 1u, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BLOCK_N;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + C::OFF_A + stage * C::A_STAGE);
                     const uint32_t b_addr = smem_u32(smem + C::OFF_B + stage * C::B_STAGE);
+                    if (elect_one()) {
                     if (C::SF_ATOMS > 0) {
                         const uint32_t sfa_addr = smem_u32(smem + C::OFF_SFA + stage * C::SFA_STAGE);
                         const uint32_t sfb_addr = smem_u32(smem + C::OFF_SFB + stage * C::SFB_STAGE);
@@ -198,7 +208,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint64_t bdesc = make_desc_sw128(b_addr);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {   // 4 x 32 bytes of K per stage
-                        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
                         if (KIND == KIND_F8) {
                             mma_f8f6f4(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accum);
                         } else if (KIND == KIND_BF16) {
@@ -214,7 +224,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
                     }
                     tc_commit(empty_bar + stage);
-                    if (kb == num_kb - 1) tc_commit(acc_full + acc);
+                    if (kb == kb1 - 1) tc_commit(acc_full + acc);
+                    }
+                    __syncwarp();
                     if (++stage == C::NUM_STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -228,8 +240,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const bool vec_ok = args.out_bf16 ? (args.ldc % 8 == 0) : (args.ldc % 4 == 0);
         bool ok = true;
         long long iter = 0;
-        for (long long t = blockIdx.x; t < tw.total && ok; t += gridDim.x, ++iter) {
-            const TileInfo ti = tw.decode(t);
+        for (long long t = blockIdx.x; t < total_items && ok; t += gridDim.x, ++iter) {
+            const TileInfo ti = tw.decode(t / split_k);
+            const int ks = static_cast<int>(t % split_k);
             const int acc = static_cast<int>(iter % C::ACC_STAGES);
             const uint32_t acc_phase = static_cast<uint32_t>((iter / C::ACC_STAGES) & 1);
             if (!mbar_wait(acc_full + acc, acc_phase, abort_flag, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
@@ -244,43 +257,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 tmem_ld_wait();
                 const int col0 = ti.n0 + c * 32;
                 if (!row_ok || col0 >= args.n) continue;
-                float f[32];
+                if (split_k > 1) {
+                    // raw fp32 partial sums of this K-slice; scales are applied by the reduction
+                    float* dst = args.partial + (static_cast<size_t>(ks) * args.m_total + row) * args.n + col0;
+                    if (args.n % 4 == 0 && col0 + 32 <= args.n) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __fmul_rn(__fmul_rn(__uint_as_float(v[i]), s1), s2);
-                    if (args.row_scale != nullptr) x = __fmul_rn(x, rs);
-                    f[i] = x;
-                }
-                if (args.col_scale != nullptr) {
-                    const float* cs = args.col_scale + static_cast<size_t>(ti.group) * args.n;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col0 + i < args.n) f[i] = __fmul_rn(f[i], cs[col0 + i]);
-                }
-                const size_t off = static_cast<size_t>(row) * args.ldc + col0;
-                if (vec_ok && col0 + 32 <= args.n) {
-                    if (args.out_bf16) {
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.c) + off);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                __nv_bfloat162 p = __floats2bfloat162_rn(f[8 * i + 2 * j], f[8 * i + 2 * j + 1]);
-                                w[j] = *reinterpret_cast<uint32_t*>(&p);
-                            }
-                            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
+                        for (int i = 0; i < 8; ++i)
+                            reinterpret_cast<float4*>(dst)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                                            __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
                     } else {
-                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.c) + off);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < args.n) dst[i] = __uint_as_float(v[i]);
                     }
                 } else {
-                    for (int i = 0; i < 32 && col0 + i < args.n; ++i) {
-                        if (args.out_bf16) static_cast<__nv_bfloat16*>(args.c)[off + i] = __float2bfloat16_rn(f[i]);
-                        else static_cast<float*>(args.c)[off + i] = f[i];
-                    }
+                    store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
                 }
             }
             tc_fence_before();
@@ -303,6 +294,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+
+// Sums the split-K partial products in slice order (deterministic) and applies the epilogue.
+// One thread per four consecutive columns of a row.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmArgs args, int split_k) {
+    const int n4 = (args.n + 3) / 4;
+    const long long id = blockIdx.x * 256ll + threadIdx.x;
+    if (id >= static_cast<long long>(args.m_total) * n4) return;
+    const int row = static_cast<int>(id / n4);
+    const int col0 = static_cast<int>(id - static_cast<long long>(row) * n4) * 4;
+    float s1 = args.s1_dev != nullptr ? *args.s1_dev : args.s1;
+    float s2 = args.s2_dev != nullptr ? *args.s2_dev : args.s2;
+    if (args.scale_product) { s1 = s1 * s2; s2 = 1.0f; }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const size_t slice = static_cast<size_t>(args.m_total) * args.n;
+    const float* p = args.partial + static_cast<size_t>(row) * args.n + col0;
+    const bool vec = args.n % 4 == 0;
+    for (int ks = 0; ks < split_k; ++ks, p += slice) {
+        if (vec) {
+            const float4 v = *reinterpret_cast<const float4*>(p);
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        } else {
+            for (int i = 0; i < 4; ++i)
+                if (col0 + i < args.n) acc[i] += p[i];
+        }
+    }
+    const float rs = args.row_scale != nullptr ? args.row_scale[row] : 1.0f;
+    for (int i = 0; i < 4; ++i) {
+        if (col0 + i >= args.n) break;
+        float x = __fmul_rn(__fmul_rn(acc[i], s1), s2);
+        if (args.row_scale != nullptr) x = __fmul_rn(x, rs);
+        if (args.col_scale != nullptr) x = __fmul_rn(x, args.col_scale[col0 + i]);
+        const size_t off = static_cast<size_t>(row) * args.ldc + col0 + i;
+        if (args.out_bf16) static_cast<__nv_bfloat16*>(args.c)[off] = __float2bfloat16_rn(x);
+        else static_cast<float*>(args.c)[off] = x;
     }
 }
 
@@ -374,9 +402,14 @@ static int launch_one(const void* A, const void* B, const GemmArgs& args, long l
         if (e != cudaSuccess) return static_cast<int>(e);
         attr_set = true;
     }
-    long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
+    const long long items = max_tiles * (args.split_k > 1 ? args.split_k : 1);
+    long long grid = items < sm_count() ? items : sm_count();
     if (grid < 1) grid = 1;
     gemm_kernel<KIND, BLOCK_N><<<static_cast<unsigned>(grid), 192, C::SMEM_BYTES, st>>>(ta, tb, args);
+    if (args.split_k > 1) {
+        const long long threads = static_cast<long long>(args.m_total) * ((args.n + 3) / 4);
+        splitk_reduce_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, st>>>(args, args.split_k);
+    }
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -392,18 +425,38 @@ static int forced_kernel() {
     return v;
 }
 
+int choose_split_k(const GemmArgs& args, long long tiles) {
+    if (args.group_offsets != nullptr || args.partial == nullptr || tiles <= 0) return 1;
+    const int num_kb = (args.k_bytes + STAGE_KB - 1) / STAGE_KB;
+    if (tiles * 2 > sm_count() || num_kb < 8) return 1;
+    long long want = sm_count() / tiles;
+    if (want > 8) want = 8;
+    if (want > num_kb / 4) want = num_kb / 4;
+    const size_t per_slice = static_cast<size_t>(args.m_total) * args.n * sizeof(float);
+    while (want > 1 && per_slice * want > args.partial_bytes) --want;
+    if (want < 2) return 1;
+    const int kb_per = (num_kb + static_cast<int>(want) - 1) / static_cast<int>(want);
+    return (num_kb + kb_per - 1) / kb_per;   // every slice non-empty
+}
+
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st) {
     if (args.m_total <= 0 || args.n <= 0) return 0;
     const int forced = forced_kernel();
     if (forced == 2 || (forced == 0 && args.m_total > 128 && args.n >= 256)) return launch_gemm_pair(kind, A, B, args, st);
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
     // Narrow outputs get 128-wide tiles (two accumulator stages, more CTAs in flight).
-    const bool narrow = args.n <= 128 || (args.n % 256 != 0 && args.n % 256 <= 128 && args.n < 1024);
-    const int block_n = narrow ? 128 : 256;
     const long long m_tiles_max = (args.m_total + BLOCK_M - 1) / BLOCK_M + groups - 1;
+    // 128-wide tiles (two accumulator stages, more CTAs in flight) for narrow outputs and
+    // whenever 256-wide tiles would leave most SMs without work.
+    const bool narrow = args.n <= 128 || (args.n % 256 != 0 && args.n % 256 <= 128 && args.n < 1024) ||
+                        m_tiles_max * ((args.n + 255) / 256) * 2 <= sm_count();
+    const int block_n = narrow ? 128 : 256;
     const long long n_tiles = (args.n + block_n - 1) / block_n;
     const long long max_tiles = m_tiles_max * n_tiles;
     if (args.band <= 0) args.band = 8;
+    // Few tiles and a long K (decode shapes): cut K so that every SM streams part of the weight.
+    // Dense problems only; needs caller scratch for the fp32 partial sums.
+    args.split_k = choose_split_k(args, max_tiles);
     switch (kind) {
         case KIND_F8:
             return narrow ? launch_one<KIND_F8, 128>(A, B, args, max_tiles, st) : launch_one<KIND_F8, 256>(A, B, args, max_tiles, st);

@@ -33,9 +33,13 @@ struct GemmArgs {
     long long ldc;
     int out_bf16;
     int band;                    // column tiles per raster band (L2 reuse)
+    int split_k;                 // > 1: K is cut into this many slices whose fp32 partial sums go to `partial`
+    float* partial;              // [split_k, m_total, n] scratch (dense problems only)
+    size_t partial_bytes;        // capacity of `partial`
     uint32_t* status;
 };
 
+int choose_split_k(const GemmArgs& args, long long tiles);
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);
 int launch_gemm_pair(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);
 int launch_gemm_fp8_groupwise(const void* A, const void* B, GemmArgs args, cudaStream_t st);

@@ -56,6 +56,9 @@ def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
             keep.append(t)
             setattr(ep, name, t.data_ptr())
     ep.out_dtype = _lib.F32 if out == torch.float32 else _lib.BF16
+    ws = _lib.workspace(dev)
+    ep.workspace = ws.data_ptr()
+    ep.workspace_bytes = ws.numel()
     return ep
 
 

@@ -85,7 +85,9 @@ int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream
 
 /* Epilogue description shared by the GEMM entry points.
  *   out = acc * scale_a * scale_b [* row_scale[m]] [* col_scale[g*N+n]]
- * scale_x is *scale_x_dev when that pointer is non-NULL, else scale_x_host. */
+ * scale_x is *scale_x_dev when that pointer is non-NULL, else scale_x_host.
+ * With a workspace, dense problems that would occupy less than half of the SMs are cut along K
+ * into up to 8 slices (each SM streams part of the weight) and summed in slice order. */
 typedef struct {
     float scale_a_host, scale_b_host;
     const float* scale_a_dev;
@@ -93,6 +95,8 @@ typedef struct {
     const float* row_scale;     /* [M_total] or NULL: per-token rescale */
     const float* col_scale;     /* [G, N]   or NULL: per-channel rescale */
     int out_dtype;              /* DSL_F32 or DSL_BF16 */
+    void* workspace;            /* optional scratch (16-byte aligned) for split-K partial sums, or NULL */
+    size_t workspace_bytes;     /* its size; decode shapes (few rows, long K) use up to 8*M*N*4 bytes */
 } dsl_epilogue;
 
 /*
