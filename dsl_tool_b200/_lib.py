@@ -20,6 +20,7 @@ F32, BF16, F16 = 0, 1, 2
 FP8_PER_TENSOR, FP8_GROUP_1X128, FP8_BLOCK_128X128 = 0, 1, 2
 FP4_NV, FP4_MX = 0, 1
 MAX_GROUPS = 1024
+STATIC_SCRATCH_BYTES = 4 << 20
 
 _ERR_NAMES = {
     -1: "a required pointer is NULL",
@@ -63,6 +64,8 @@ _SIGNATURES = {
                                     ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_gemm_fp4": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i, _vp, _i,
                           ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_gemm_fp4_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i,
+                                         ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),
 }

@@ -140,6 +140,23 @@ int dsl_gemm_fp4(const uint8_t* A, const uint8_t* B, const uint8_t* sfa, const u
                  long long ldc, long long M_total, int N, int K, const int* group_offsets, int groups,
                  const dsl_epilogue* ep, uint32_t* status, void* stream);
 
+/*
+ * dsl_gemm_fp4 for callers that cannot allocate device memory (no counterpart in the
+ * reference).  Same operands and result as dsl_gemm_fp4 on a dense problem, but the split-K
+ * scratch is a fixed DSL_STATIC_SCRATCH_BYTES array inside the library instead of
+ * ep->workspace (which is ignored), so nothing but inputs and outputs is passed and the call
+ * performs no allocation.  Meant for decode-sized problems: it returns DSL_ERR_TOO_LARGE unless
+ * 2 * M * N * 4 bytes fit in the array.  The first call on each device looks up the array's
+ * device address (cudaGetSymbolAddress); make that call before any stream capture.  All calls
+ * share the one array and it keeps the previous call's contents; every element a call reads
+ * has been written by that call first, so nothing needs clearing, but two calls that overlap
+ * on the GPU (different streams) race on it.
+ */
+#define DSL_STATIC_SCRATCH_BYTES (4u << 20)
+int dsl_gemm_fp4_static_scratch(const uint8_t* A, const uint8_t* B, const uint8_t* sfa, const uint8_t* sfb,
+                                int format, void* C, long long ldc, long long M, int N, int K,
+                                const dsl_epilogue* ep, uint32_t* status, void* stream);
+
 /* Runs one bounded wait on a barrier nothing ever signals and reports DSL_ST_TIMEOUT_TEST
  * in *status after about `limit_us` microseconds: exercises the give-up path without
  * faulting or hanging the device. */
