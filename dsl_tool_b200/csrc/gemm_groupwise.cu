@@ -16,6 +16,8 @@
 //               the stage back to the producer and the partial buffer to the epilogue
 //   warps 2-9   epilogue: warp w owns tensor-memory lanes 32*(w%4).. and 128 of the 256 columns
 #include <cuda_bf16.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "gemm.cuh"
 #include "gemm_tiles.cuh"
@@ -287,6 +289,9 @@ static int launch_gw(const void* A, const void* B, const GemmArgs& args, cudaStr
 
 int launch_gemm_fp8_groupwise(const void* A, const void* B, GemmArgs args, cudaStream_t st) {
     if (args.m_total <= 0 || args.n <= 0) return 0;
+    const char* forced = getenv("DSLGEMM_KERNEL");
+    const bool force_1cta = forced != nullptr && strcmp(forced, "1cta") == 0;
+    if (!force_1cta && args.m_total > 128 && args.n >= 256) return launch_gemm_fp8_groupwise_pair(A, B, args, st);
     if (args.band <= 0) args.band = 8;
     return args.sb_block ? launch_gw<true>(A, B, args, st) : launch_gw<false>(A, B, args, st);
 }

@@ -1,0 +1,335 @@
+// FP8 E4M3 GEMM with fp32 scales per 128 K-elements on a CTA pair (cta_group::2), dense and grouped:
+//
+//   C[m, n] = sum_g ( sum_{k in group g} A[m,k] * B[n,k] ) * sa[m, g] * sb[g, n]
+//
+// (fp8_gemm_groupwise_kernel of the reference, cuda/gemm/fp8_gemm.cu:69-99, group size 128 = one
+// shared-memory stage of K).  Same pair structure as gemm_pair.cu: each CTA loads its own halves of
+// the 256x256 tile, the leader issues tcgen05.mma.cta_group::2.  fp32 scales cannot ride in the
+// MMA, so every K-group's 128x256 partial product (per CTA) lands in one of two tensor-memory
+// buffers and eight epilogue warps promote it into register accumulators (acc += p * sa * sb)
+// while the tensor cores fill the other buffer.  The promotion streams tensor memory in 16-column
+// pieces, the next piece in flight while the current one is multiplied.
+//
+//   warp 0     TMA producer          warp 1   leader: MMA issuer / peer: "stage landed" forwarder
+//   warps 2-9  promotion + epilogue: warp w owns lanes 32*(w%4).. and 128 of the 256 columns
+#include <cuda_bf16.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "gemm.cuh"
+#include "gemm_epilogue.cuh"
+#include "gemm_tiles.cuh"
+#include "ptx.cuh"
+
+namespace dsl {
+namespace gwp {
+
+constexpr int TILE_M = 256;
+constexpr int TILE_N = 256;
+constexpr int A_STAGE = 128 * STAGE_KB;
+constexpr int B_STAGE = 128 * STAGE_KB;
+constexpr int NUM_STAGES = 6;
+constexpr int OFF_A = 0;
+constexpr int OFF_B = NUM_STAGES * A_STAGE;
+constexpr int OFF_BAR = OFF_B + NUM_STAGES * B_STAGE;
+constexpr int NUM_BARS = 3 * NUM_STAGES + 4;
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+constexpr int OFF_TABLE = OFF_MISC + 16;
+constexpr int SMEM_BYTES = OFF_TABLE + 2 * (DSL_MAX_GROUPS + 1) * 4 + 1024;
+constexpr int THREADS = 320;
+static_assert(SMEM_BYTES > 116224 && SMEM_BYTES <= 232448, "one CTA per SM");
+
+struct Tile {
+    int group, row0, row_end, n0;
+};
+
+struct Walker {
+    const int* offs;
+    const int* tile0;
+    int groups, m_tiles, n_tiles, band;
+    long long total;
+    __device__ __forceinline__ Tile decode(long long t) const {
+        const long long per_band = static_cast<long long>(m_tiles) * band;
+        const int b = static_cast<int>(t / per_band);
+        const int r = static_cast<int>(t - b * per_band);
+        const int nb0 = b * band;
+        const int wb = min(band, n_tiles - nb0);
+        const int mt = r / wb;
+        const int nt = nb0 + (r - mt * wb);
+        int lo = 0, hi = groups;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (tile0[mid] <= mt) lo = mid; else hi = mid;
+        }
+        Tile ti;
+        ti.group = lo;
+        ti.row0 = offs[lo] + (mt - tile0[lo]) * TILE_M;
+        ti.row_end = offs[lo + 1];
+        ti.n0 = nt * TILE_N;
+        return ti;
+    }
+};
+
+}  // namespace gwp
+
+template <bool SB_BLOCK>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gwp::THREADS, 1)
+gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                               const GemmArgs args) {
+    using namespace gwp;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+    uint64_t* peer_full = full_bar + NUM_STAGES;      // leader only
+    uint64_t* empty_bar = peer_full + NUM_STAGES;
+    uint64_t* part_full = empty_bar + NUM_STAGES;     // [2] partial product complete (both CTAs)
+    uint64_t* part_empty = part_full + 2;             // [2] leader only: all 16 promotion warps drained the buffer
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
+    int* s_offs = reinterpret_cast<int*>(smem + OFF_TABLE);
+    int* s_tile0 = s_offs + (DSL_MAX_GROUPS + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
+    const long long pair_id = blockIdx.x >> 1;
+    const long long num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NUM_STAGES; ++i) {
+            mbar_init(full_bar + i, 1);
+            mbar_init(peer_full + i, 1);
+            mbar_init(empty_bar + i, 1);
+        }
+        for (int i = 0; i < 2; ++i) { mbar_init(part_full + i, 1); mbar_init(part_empty + i, 16); }
+        *abort_flag = 0;
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    for (int g = threadIdx.x; g <= groups; g += blockDim.x)
+        s_offs[g] = args.group_offsets != nullptr ? args.group_offsets[g] : (g == 0 ? 0 : args.m_total);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int g = 0; g < groups; ++g) {
+            s_tile0[g] = t;
+            const int rows = s_offs[g + 1] - s_offs[g];
+            if (rows > 0) t += (rows + TILE_M - 1) / TILE_M;
+        }
+        s_tile0[groups] = t;
+    }
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) tmem_alloc_pair(tmem_ptr, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    Walker tw;
+    tw.offs = s_offs;
+    tw.tile0 = s_tile0;
+    tw.groups = groups;
+    tw.m_tiles = s_tile0[groups];
+    tw.n_tiles = (args.n + TILE_N - 1) / TILE_N;
+    tw.band = args.band < 1 ? 1 : args.band;
+    tw.total = static_cast<long long>(tw.m_tiles) * tw.n_tiles;
+    const int num_kb = args.k_bytes / STAGE_KB;   // K % 128 == 0
+
+    if (warp == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+            const Tile ti = tw.decode(t);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait_cluster(empty_bar + stage, phase ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(full_bar + stage, A_STAGE + B_STAGE);
+                    tma_load_2d(smem + OFF_A + stage * A_STAGE, &tmap_a, full_bar + stage, kb * STAGE_KB,
+                                ti.row0 + 128 * static_cast<int>(rank));
+                    tma_load_3d(smem + OFF_B + stage * B_STAGE, &tmap_b, full_bar + stage, kb * STAGE_KB,
+                                ti.n0 + 128 * static_cast<int>(rank), ti.group);
+                }
+                __syncwarp();
+                if (++stage == NUM_STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0) {
+            const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(TILE_N >> 3) << 17) |
+                                   (static_cast<uint32_t>(TILE_M >> 4) << 24);   // E4M3 x E4M3 -> fp32
+            int stage = 0;
+            uint32_t phase = 0;
+            long long step = 0;
+            bool ok = true;
+            for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+                for (int kb = 0; kb < num_kb; ++kb, ++step) {
+                    const int p = static_cast<int>(step & 1);
+                    const uint32_t pphase = static_cast<uint32_t>((step >> 1) & 1);
+                    if (!mbar_wait_cluster(part_empty + p, pphase ^ 1u, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    if (!mbar_wait(full_bar + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    if (!mbar_wait_cluster(peer_full + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = make_desc_sw128(smem_u32(smem + OFF_A + stage * A_STAGE));
+                    const uint64_t bdesc = make_desc_sw128(smem_u32(smem + OFF_B + stage * B_STAGE));
+                    if (elect_one()) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            mma_f8f6f4_pair(tmem_base + p * TILE_N, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                        tc_commit_pair(empty_bar + stage);
+                        tc_commit_pair(part_full + p);
+                    }
+                    __syncwarp();
+                    if (++stage == NUM_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        } else {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_bar + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    if (lane == 0) mbar_arrive_cluster(peer_full + stage, 0);
+                    __syncwarp();
+                    if (++stage == NUM_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else {
+        // ================= promotion + epilogue =================
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const float s1 = args.s1_dev != nullptr ? *args.s1_dev : args.s1;
+        const float s2 = args.s2_dev != nullptr ? *args.s2_dev : args.s2;
+        const bool vec_ok = args.out_bf16 ? (args.ldc % 8 == 0) : (args.ldc % 4 == 0);
+        const int nb128 = (args.n + 127) / 128;
+        long long step = 0;
+        bool ok = true;
+        for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+            const Tile ti = tw.decode(t);
+            const int row = ti.row0 + 128 * static_cast<int>(rank) + quad * 32 + lane;
+            const bool row_ok = row < ti.row_end;
+            const int col_base = ti.n0 + half * 128;
+            const float* sa_row = args.gsa + static_cast<size_t>(row_ok ? row : ti.row0) * num_kb;
+            const float* sb_ptr;
+            if (SB_BLOCK) {
+                const int nb = min(col_base / 128, nb128 - 1);
+                sb_ptr = args.gsb + (static_cast<size_t>(ti.group) * nb128 + nb) * num_kb;
+            } else {
+                sb_ptr = args.gsb + static_cast<size_t>(ti.group) * num_kb * args.n;
+            }
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+            float sa_next = __ldg(sa_row);
+            float sb_next = SB_BLOCK ? __ldg(sb_ptr) : 0.f;
+            for (int kb = 0; kb < num_kb; ++kb, ++step) {
+                const float sa = sa_next;
+                const float s = SB_BLOCK ? __fmul_rn(sa, sb_next) : 0.f;
+                if (kb + 1 < num_kb) {   // next group's scales are fetched while this one is promoted
+                    sa_next = __ldg(sa_row + kb + 1);
+                    if (SB_BLOCK) sb_next = __ldg(sb_ptr + kb + 1);
+                }
+                const int p = static_cast<int>(step & 1);
+                const uint32_t pphase = static_cast<uint32_t>((step >> 1) & 1);
+                if (!mbar_wait_cluster(part_full + p, pphase, abort_flag, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + p * TILE_N + half * 128 + (static_cast<uint32_t>(quad * 32) << 16);
+                uint32_t buf[2][16];
+                tmem_ld_32x32b_x16(taddr, buf[0]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    tmem_ld_wait();
+                    if (c + 1 < 8) tmem_ld_32x32b_x16(taddr + (c + 1) * 16, buf[(c + 1) & 1]);
+                    if (SB_BLOCK) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            acc[c * 16 + i] = fmaf(__uint_as_float(buf[c & 1][i]), s, acc[c * 16 + i]);
+                    } else {
+                        const float* sbrow = sb_ptr + static_cast<size_t>(kb) * args.n;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const int col = col_base + c * 16 + i;
+                            const float sb = col < args.n ? __ldg(sbrow + col) : 0.f;
+                            acc[c * 16 + i] = fmaf(__fmul_rn(__uint_as_float(buf[c & 1][i]), sa), sb, acc[c * 16 + i]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(part_empty + p, 0);
+            }
+            if (!ok) break;
+            if (!row_ok) continue;
+            const float rs = args.row_scale != nullptr ? args.row_scale[row] : 1.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int col0 = col_base + c * 32;
+                if (col0 >= args.n) continue;
+                uint32_t v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(acc[c * 32 + i]);
+                store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    const uint32_t aborted = *abort_flag;
+    if (aborted != 0) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(2000);
+        if (threadIdx.x == 0 && args.status != nullptr) atomicOr(args.status, aborted);
+    }
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+template <bool SB_BLOCK>
+static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
+    CUtensorMap ta, tb;
+    const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
+    if (!make_tmap_u8(&ta, A, args.k_bytes, args.m_total, 0, STAGE_KB, 128)) return DSL_ERR_DRIVER;
+    if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, 128)) return DSL_ERR_DRIVER;
+    static int max_clusters = 0;
+    if (max_clusters == 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_pair_kernel<SB_BLOCK>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, gwp::SMEM_BYTES);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(sms > 1 ? (sms / 2) * 2 : 2));
+        cfg.blockDim = dim3(gwp::THREADS);
+        cfg.dynamicSmemBytes = gwp::SMEM_BYTES;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_fp8_groupwise_pair_kernel<SB_BLOCK>, &cfg);
+        max_clusters = (e == cudaSuccess && n > 0) ? n : (sms > 1 ? sms / 2 : 1);
+        (void)cudaGetLastError();
+    }
+    const long long m_tiles_max = (args.m_total + gwp::TILE_M - 1) / gwp::TILE_M + groups - 1;
+    const long long max_tiles = m_tiles_max * ((args.n + gwp::TILE_N - 1) / gwp::TILE_N);
+    long long clusters = max_tiles < max_clusters ? max_tiles : max_clusters;
+    if (clusters < 1) clusters = 1;
+    gemm_fp8_groupwise_pair_kernel<SB_BLOCK><<<static_cast<unsigned>(2 * clusters), gwp::THREADS, gwp::SMEM_BYTES, st>>>(ta, tb, args);
+    return static_cast<int>(cudaGetLastError());
+}
+
+int launch_gemm_fp8_groupwise_pair(const void* A, const void* B, GemmArgs args, cudaStream_t st) {
+    if (args.m_total <= 0 || args.n <= 0) return 0;
+    if (args.band <= 0) args.band = 8;
+    return args.sb_block ? launch_gw_pair<true>(A, B, args, st) : launch_gw_pair<false>(A, B, args, st);
+}
+
+}  // namespace dsl
