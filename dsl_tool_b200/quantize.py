@@ -136,11 +136,15 @@ class PackedWeight:
     k: int
 
 
-def pack_weight(w: torch.Tensor, format: str, layout: str = "nk") -> PackedWeight:
+def pack_weight(w: torch.Tensor, format: str, layout: str = "nk",
+                global_scale: Union[None, float, torch.Tensor] = None) -> PackedWeight:
     """Quantise a weight for the GEMM entry points.
 
     w is [N, K] / [G, N, K] (layout "nk") or the reference's [K, N] / [G, K, N] (layout "kn",
-    cuda/gemm/fp8_gemm.cu:29-35); it is made K-major first.
+    cuda/gemm/fp8_gemm.cu:29-35); it is made K-major first.  `global_scale` (NVFP4 only) fixes the
+    fp32 global scale instead of deriving it from this tensor's amax - pass the unsharded tensor's
+    amax/2688 when packing a column or expert shard so that every shard quantises exactly as the
+    whole weight would.
     """
     dev = _lib.require_cuda(w)
     if layout not in ("nk", "kn"):
@@ -170,11 +174,13 @@ def pack_weight(w: torch.Tensor, format: str, layout: str = "nk") -> PackedWeigh
         return PackedWeight("fp8_block128", q, s.contiguous(), None, G, N, K)
     if format in ("nvfp4", "mxfp4"):
         if G == 1 or N % 128 == 0:
-            q, sf, gs = quantize_fp4(flat, format)
+            q, sf, gs = quantize_fp4(flat, format, global_scale=global_scale if format == "nvfp4" else None)
         else:   # every expert's scales start a fresh 128-row tile
             offs = torch.arange(G + 1, dtype=torch.int32, device=dev) * N
             gs_val = None
-            if format == "nvfp4":
+            if format == "nvfp4" and global_scale is not None:
+                gs_val = global_scale
+            elif format == "nvfp4":
                 gs_val = (flat.abs().amax().float() / 2688.0)
                 gs_val = torch.where(gs_val == 0, torch.ones_like(gs_val), gs_val)
             # the grouped layout packs groups back to back in whole tiles, i.e. exactly

@@ -1,0 +1,65 @@
+"""Column-parallel / expert-parallel split on real GPUs with the CUDA kernels and an NCCL gather.
+Runs as child processes, one per GPU; skipped with fewer than two GPUs."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["REPO_ROOT"])
+from dsl_tool_b200 import linear, pack_weight
+from dsl_tool_b200.sharding import ColumnParallelLinear, ExpertParallelGroupedLinear, shard_weight_columns, shard_weight_experts
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+g = torch.Generator(device="cuda").manual_seed(0)
+x = torch.randn(300, 512, generator=g, device="cuda").bfloat16()
+w = (torch.randn(1024, 512, generator=g, device="cuda") * 0.02).bfloat16()
+ok = True
+for fmt in ("nvfp4", "fp8_block128"):
+    full = linear(x, pack_weight(w, fmt), out_dtype="float32")
+    gs = w.float().abs().amax() / 2688.0 if fmt == "nvfp4" else None     # the whole weight's global scale
+    lin = ColumnParallelLinear(pack_weight(shard_weight_columns(w, rank, world).contiguous(), fmt, global_scale=gs), 1024, linear)
+    y = lin.forward(x, gather=True, out_dtype="float32")
+    err = float((y - full).norm() / full.norm())
+    print(rank, fmt, "column-parallel relF", err, tuple(y.shape), flush=True)
+    ok &= err < 1e-6
+G = 4
+wg = (torch.randn(G, 256, 512, generator=g, device="cuda") * 0.02).bfloat16()
+offs = [0, 100, 100, 180, 300]
+full = linear(x, pack_weight(wg, "mxfp4"), expert_offsets=torch.tensor(offs, dtype=torch.int32, device="cuda"), out_dtype="float32")
+ep = ExpertParallelGroupedLinear(pack_weight(shard_weight_experts(wg, rank, world).contiguous(), "mxfp4"), G, linear)
+y = ep.forward_from_global(x, offs, gather=True, out_dtype="float32")
+err = float((y - full).norm() / full.norm())
+print(rank, "expert-parallel relF", err, tuple(y.shape), flush=True)
+ok &= err < 1e-6
+torch.cuda.synchronize()
+dist.destroy_process_group()
+sys.exit(0 if ok else 3)
+'''
+
+
+def test_two_gpu_split_matches_single_gpu(cuda_device, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   REPO_ROOT=root, NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(o[-1500:] for o in outs)
