@@ -26,8 +26,13 @@ namespace pr {
 
 constexpr int TILE_M = 256;
 constexpr int TILE_N = 256;
-constexpr int SFA_COL = 256;
-constexpr int SFB_COL = 272;
+// Tensor-memory columns.  Plain kinds: two 256-column accumulators.  Block-scaled kinds need 48
+// columns for the scale factors, so their two accumulators overlap in columns [192, 256): tile i
+// uses [0, 256) or [192, 448) in turn, and the epilogue reads the shared 64 columns first and
+// releases them, so the next tile's MMAs start while the other 192 columns are still being read.
+constexpr int SFA_COL = 448;
+constexpr int SFB_COL = 464;
+constexpr int OVERLAP_COL = 192;
 
 template <int KIND>
 struct Cfg {
@@ -37,13 +42,14 @@ struct Cfg {
     static constexpr int SFA_STAGE = SF_ATOMS * 512;          // this CTA's 128 A rows
     static constexpr int SFB_STAGE = 2 * SF_ATOMS * 512;      // all 256 output columns
     static constexpr int NUM_STAGES = SF_ATOMS > 0 ? 5 : 6;
-    static constexpr int ACC_STAGES = SF_ATOMS > 0 ? 1 : 2;
+    static constexpr int ACC_STAGES = 2;
+    static constexpr int ACC1_COL = SF_ATOMS > 0 ? OVERLAP_COL : TILE_N;
     static constexpr int OFF_A = 0;
     static constexpr int OFF_B = OFF_A + NUM_STAGES * A_STAGE;
     static constexpr int OFF_SFA = OFF_B + NUM_STAGES * B_STAGE;
     static constexpr int OFF_SFB = OFF_SFA + NUM_STAGES * SFA_STAGE;
     static constexpr int OFF_BAR = OFF_SFB + NUM_STAGES * SFB_STAGE;
-    static constexpr int NUM_BARS = 3 * NUM_STAGES + 2 * ACC_STAGES;
+    static constexpr int NUM_BARS = 3 * NUM_STAGES + 2 * ACC_STAGES + 1;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
     static constexpr int OFF_TABLE = OFF_MISC + 16;                         // offs, tile0, sftile0
     static constexpr int SMEM_BYTES = OFF_TABLE + 3 * (DSL_MAX_GROUPS + 1) * 4 + 1024;
@@ -98,6 +104,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint64_t* empty_bar = peer_full + C::NUM_STAGES;                       // MMAs reading the stage are done
     uint64_t* acc_full = empty_bar + C::NUM_STAGES;
     uint64_t* acc_empty = acc_full + C::ACC_STAGES;                        // leader only: both epilogues drained
+    uint64_t* ovl_free = acc_empty + C::ACC_STAGES;                        // leader only: shared columns of the previous tile read
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 4);
     int* s_offs = reinterpret_cast<int*>(smem + C::OFF_TABLE);
@@ -118,6 +125,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_init(empty_bar + i, 1);
         }
         for (int i = 0; i < C::ACC_STAGES; ++i) { mbar_init(acc_full + i, 1); mbar_init(acc_empty + i, 8); }
+        mbar_init(ovl_free, 8);
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
@@ -228,8 +236,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int acc = static_cast<int>(iter % C::ACC_STAGES);
                 const uint32_t acc_phase = static_cast<uint32_t>((iter / C::ACC_STAGES) & 1);
                 if (!mbar_wait_cluster(acc_empty + acc, acc_phase ^ 1u, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                if (C::SF_ATOMS > 0 && iter > 0 &&
+                    !mbar_wait_cluster(ovl_free, static_cast<uint32_t>((iter - 1) & 1), abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * pr::TILE_N;
+                const uint32_t d_tmem = tmem_base + acc * C::ACC1_COL;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     if (!mbar_wait_cluster(peer_full + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
@@ -308,10 +318,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const bool row_ok = row < ti.row_end;
             const float rs = (row_ok && args.row_scale != nullptr) ? args.row_scale[row] : 1.0f;
 #pragma unroll 1
-            for (int c = 0; c < pr::TILE_N / 32; ++c) {
+            for (int j = 0; j < pr::TILE_N / 32; ++j) {
+                // block-scaled kinds: the 64 columns shared with the other accumulator go first
+                const int c = (C::SF_ATOMS > 0 && acc == 0) ? ((j + 6) & 7) : j;
                 uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + acc * pr::TILE_N + c * 32 + (static_cast<uint32_t>(quad * 32) << 16), v);
+                tmem_ld_32x32b_x32(tmem_base + acc * C::ACC1_COL + c * 32 + (static_cast<uint32_t>(quad * 32) << 16), v);
                 tmem_ld_wait();
+                if (C::SF_ATOMS > 0 && j == 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(ovl_free, 0);
+                }
                 const int col0 = ti.n0 + c * 32;
                 if (row_ok && col0 < args.n) store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
             }
