@@ -49,6 +49,9 @@ WORKLOADS = {
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
 }
 DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
+# dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from an ncu capture of the
+# full-size workload (profiles/): bytes.  None where no capture exists.
+NCU_TRAFFIC = {"fp8_groupwise_llama8b_mlp": 77.1e6 + 74.9e6}
 PEAK_MULT = {"fp8": 2.0, "fp8_block128": 2.0, "nvfp4": 4.0, "mxfp4": 4.0, "bf16": 1.0}
 
 
@@ -344,7 +347,7 @@ def main():
                    "step": "activation quantise + GEMM, weights quantised once",
                    "l2": f"inputs rotate over {args.sets} sets (larger than the 126 MB L2)"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(args.workload),
                      "kernel": "gemm", "kernel_ms": gemm_ms, "quant_kernel_ms": quant_ms,
                      "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"},
         "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",

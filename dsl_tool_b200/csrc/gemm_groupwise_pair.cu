@@ -245,7 +245,13 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     tmem_ld_wait();
-                    if (c + 1 < 8) tmem_ld_32x32b_x16(taddr + (c + 1) * 16, buf[(c + 1) & 1]);
+                    if (c + 1 < 8) {
+                        tmem_ld_32x32b_x16(taddr + (c + 1) * 16, buf[(c + 1) & 1]);
+                    } else {   // the whole partial product is in registers: hand the buffer back now
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(part_empty + p, 0);
+                    }
                     if (SB_BLOCK) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
@@ -260,9 +266,6 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                         }
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(part_empty + p, 0);
             }
             if (!ok) break;
             if (!row_ok) continue;
