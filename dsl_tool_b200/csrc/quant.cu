@@ -79,12 +79,26 @@ __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
     float s = __fdiv_rn(amax, 448.0f);
     return s < 1e-12f ? 1e-12f : s;
 }
+// x / s for the E4M3 conversion, bit-identical in effect to the IEEE quotient but cheaper: the
+// product x * rcp(s) is within 2 ulp of the correctly rounded quotient, so both round to the
+// same E4M3 code unless the product lies within 2 ulp of a rounding boundary of the 3-bit
+// mantissa (low 20 bits = 0x80000) or in the subnormal range of E4M3 (|r| < 2^-6, where the
+// boundaries sit elsewhere); only those rare elements take the true division.
+__device__ __forceinline__ float div_for_e4m3(float x, float s, float inv) {
+    float r = __fmul_rn(x, inv);
+    const uint32_t b = __float_as_uint(r);
+    const bool near_tie = ((b & 0xFFFFFu) - 0x7FFFEu) <= 4u;
+    const bool small = (b & 0x7FFFFFFFu) < 0x3C800000u;   // |r| < 2^-6, zero included
+    if (near_tie || small) r = __fdiv_rn(x, s);
+    return r;
+}
 __device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
+    const float inv = __frcp_rn(s);
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        uint32_t lo = cvt_e4m3x2(__fdiv_rn(v[4 * i], s), __fdiv_rn(v[4 * i + 1], s));
-        uint32_t hi = cvt_e4m3x2(__fdiv_rn(v[4 * i + 2], s), __fdiv_rn(v[4 * i + 3], s));
+        uint32_t lo = cvt_e4m3x2(div_for_e4m3(v[4 * i], s, inv), div_for_e4m3(v[4 * i + 1], s, inv));
+        uint32_t hi = cvt_e4m3x2(div_for_e4m3(v[4 * i + 2], s, inv), div_for_e4m3(v[4 * i + 3], s, inv));
         w[i] = lo | (hi << 16);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
@@ -306,9 +320,20 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __res
         blk = kc >> 1;
         writer = (kc & 1) == 0;
     }
-    if (valid) {
-        *reinterpret_cast<uint2*>(q + static_cast<size_t>(id) * 8) = quant16_e2m1(v, inv);
-        if (writer) sf[sfi(row, blk)] = static_cast<uint8_t>(sfb);
+    if (valid) *reinterpret_cast<uint2*>(q + static_cast<size_t>(id) * 8) = quant16_e2m1(v, inv);
+    // Scale bytes: four consecutive K-blocks of a row are four consecutive bytes of the tile
+    // layout, so when the row length allows it one lane stores all four as a word.
+    constexpr int LANES_PER_BLK = FMT == 0 ? 1 : 2;
+    const bool packed = (cpr % (4 * LANES_PER_BLK)) == 0;   // uniform over the grid
+    if (packed) {
+        uint32_t word = sfb;
+        word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 1 * LANES_PER_BLK) << 8;
+        word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 2 * LANES_PER_BLK) << 16;
+        word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 3 * LANES_PER_BLK) << 24;
+        if (valid && (kc % (4 * LANES_PER_BLK)) == 0)
+            *reinterpret_cast<uint32_t*>(sf + sfi(row, blk)) = word;
+    } else if (valid && writer) {
+        sf[sfi(row, blk)] = static_cast<uint8_t>(sfb);
     }
 }
 
