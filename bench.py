@@ -241,6 +241,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sets", type=int, default=4, help="rotating input sets (keeps operands out of L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true",
+                    help="replay each step (quantise + GEMM) from a CUDA graph: removes host launch gaps, "
+                         "which dominate the decode-sized workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -291,10 +294,35 @@ def main():
     t_end.record()
     barrier()
     total_ms = t_start.elapsed_time(t_end)
-    clocks = sampler.stop() if rank == 0 else None
-    _lib.check_status(device)
     gemm_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
     quant_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    graph_ms = None
+    if args.graph:
+        # same steps, captured once per input set and replayed: device time without host gaps
+        side = torch.cuda.Stream()
+        graphs = []
+        with torch.cuda.stream(side):
+            for i in range(args.sets):
+                gemm(i, quant(i))                     # this stream's scratch exists before capture
+            torch.cuda.synchronize()
+            for i in range(args.sets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    keep = gemm(i, quant(i))
+                graphs.append((g, keep))
+            for i in range(W):
+                graphs[i % args.sets][0].replay()
+            barrier()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            for i in range(K_steps):
+                graphs[i % args.sets][0].replay()
+            g1.record()
+            barrier()
+            graph_ms = g0.elapsed_time(g1) / K_steps
+        total_ms = graph_ms * K_steps
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status(device)
 
     # ---- end to end: activations from pinned host memory, result back to the host -----------
     host_a = [torch.empty_like(wl["acts"][0], device="cpu").pin_memory() for _ in range(2)]
@@ -338,6 +366,17 @@ def main():
     kind = wl["kind"]
     achieved = wl["flops"] / (gemm_ms * 1e-3) / 1e12
     peak = bf16_peak * PEAK_MULT[kind]
+    decode = wl["M"] <= 128 and not wl["moe"]
+    if decode and kind in ("nvfp4", "mxfp4"):
+        # weight streaming: the step is bound by HBM; algorithmic bytes = operands + scales + output, each once
+        sfdiv = 16 if kind == "nvfp4" else 32
+        step_bytes = (wl["M"] + wl["N"]) * wl["K"] * (0.5 + 1.0 / sfdiv) + 2.0 * wl["M"] * wl["N"] + 2.0 * wl["M"] * wl["K"]
+        hbm = {"bound": "hbm", "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+               "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+               "kernel": "quantise + split-K gemm + reduce (whole step)", "bytes_per_step": step_bytes,
+               "peak_basis": f"{basis} HBM copy {hbm_peak} GB/s"}
+    else:
+        hbm = None
     line = {
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -353,9 +392,15 @@ def main():
         "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": wl["M"] * wl["N"] * 2,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": 2 * K_steps if kind != "bf16" else K_steps,
+        # kernels of this library per step: quantiser passes + GEMM (+ split-K reduction on decode shapes)
+        "gpu_launches": K_steps * ({"fp8": 3, "fp8_block128": 2, "nvfp4": 4, "mxfp4": 2, "bf16": 1}[kind]
+                                   + (1 if decode else 0)),
+        "cuda_graph": bool(args.graph),
         "clocks": clocks,
     }
+    if hbm is not None:
+        line["roofline_tensor"] = line["roofline"]
+        line["roofline"] = hbm
     if not args.no_cpu_baseline and world == 1:
         rows = 512
         val, cores, dt, sample = cpu_baseline(args.workload, rows)

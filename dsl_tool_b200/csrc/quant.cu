@@ -137,6 +137,28 @@ __global__ void nvfp4_global_scale_kernel(const uint32_t* amax_bits, float* gs) 
     *gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
 }
 
+// Division-free thread -> (row, 16-element chunk) mapping shared by the row-wise quantisers.
+// A block of 256 threads covers `rows_per_block` rows x 2^log2_cp chunk slots (slots past the
+// row's real chunk count idle); rows longer than 256 chunks take several blocks along grid.y.
+struct RowMap {
+    int log2_cp;          // chunk slots per row inside a block (power of two, <= 256)
+    int rows_per_block;   // 256 >> log2_cp
+};
+static inline RowMap make_row_map(long long cols, int min_log2) {
+    const long long cpr = cols / 16;
+    int l = min_log2;
+    while ((1ll << l) < cpr && l < 8) ++l;
+    RowMap m;
+    m.log2_cp = l;
+    m.rows_per_block = 256 >> l;
+    return m;
+}
+static inline dim3 row_map_grid(const RowMap& m, long long rows, long long cols) {
+    const long long cpr = cols / 16;
+    return dim3(static_cast<unsigned>((rows + m.rows_per_block - 1) / m.rows_per_block),
+                static_cast<unsigned>((cpr + 255) / 256));
+}
+
 // ---- FP8 ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -164,32 +186,26 @@ quant_fp8_tensor_kernel(const T* __restrict__ x, size_t n, const uint32_t* amax_
 template <typename T>
 __global__ void __launch_bounds__(256)
 quant_fp8_1x128_kernel(const T* __restrict__ x, long long M, int K, uint8_t* __restrict__ q,
-                       float* __restrict__ scales) {
+                       float* __restrict__ scales, int log2_cp) {
+    const int cpr = K / 16;
     const int ng = (K + 127) / 128;
-    const long long total = M * ng;
-    const long long gthread = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    const long long gid = gthread >> 3;
-    const int j = static_cast<int>(gthread & 7);
-    long long row = 0;
-    int kg = 0;
-    bool valid = gid < total;
-    if (valid) {
-        row = gid / ng;
-        kg = static_cast<int>(gid - row * ng);
-        valid = kg * 128 + j * 16 < K;
-    }
+    const long long row = blockIdx.x * static_cast<long long>(256 >> log2_cp) + (threadIdx.x >> log2_cp);
+    const int kc = blockIdx.y * 256 + (threadIdx.x & ((1 << log2_cp) - 1));
+    const bool valid = row < M && kc < cpr;
     float v[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = 0.f;
-    const size_t off = static_cast<size_t>(row) * K + kg * 128 + j * 16;
+    const size_t off = static_cast<size_t>(row) * K + static_cast<size_t>(kc) * 16;
     if (valid) load16<T>(x + off, v);
-    float m = amax16(v);
+    float m = amax16(v);   // the 8 lanes of a group are adjacent (slots per row are a multiple of 8)
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
     const float s = fp8_scale_from_amax(m);
-    if (valid) *reinterpret_cast<uint4*>(q + off) = quant16_e4m3(v, s);
-    if (j == 0 && gid < total) scales[gid] = s;
+    if (valid) {
+        *reinterpret_cast<uint4*>(q + off) = quant16_e4m3(v, s);
+        if ((kc & 7) == 0) scales[static_cast<size_t>(row) * ng + (kc >> 3)] = s;
+    }
 }
 
 // 128 x 128 blocks of a K-major [N, K] weight: one CTA per block, 64 elements per thread.
@@ -259,7 +275,7 @@ template <typename T, int FMT>   // FMT 0: NVFP4 (block 16, UE4M3 + global scale
 __global__ void __launch_bounds__(256)
 quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __restrict__ gs_ptr,
                  uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
-                 int num_groups) {
+                 int num_groups, int log2_cp) {
     __shared__ int s_offs[kMaxGroups + 1];
     __shared__ int s_tile0[kMaxGroups + 1];
     SfIndexer sfi;
@@ -284,19 +300,18 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __res
         sfi.tile0 = s_tile0;
     }
     const int cpr = K / 16;   // 16-element chunks per row
-    const long long total = M * cpr;
-    const long long id = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    const bool valid = id < total;
-    long long row = 0;
-    int kc = 0;
+    const int rpb = 256 >> log2_cp;
+    const long long row_blocks = (M + rpb - 1) / rpb;
+    const int kc = blockIdx.y * 256 + (threadIdx.x & ((1 << log2_cp) - 1));
+    // grid-stride over row blocks: the group tables above are built once per CTA, not once per row
+    for (long long rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+    const long long row = rb * rpb + (threadIdx.x >> log2_cp);
+    const bool valid = row < M && kc < cpr;
+    const size_t id = static_cast<size_t>(row) * cpr + kc;
     float v[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = 0.f;
-    if (valid) {
-        row = id / cpr;
-        kc = static_cast<int>(id - row * cpr);
-        load16<T>(x + static_cast<size_t>(id) * 16, v);
-    }
+    if (valid) load16<T>(x + id * 16, v);
     float m = amax16(v);
     float inv;
     uint32_t sfb;
@@ -320,7 +335,7 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __res
         blk = kc >> 1;
         writer = (kc & 1) == 0;
     }
-    if (valid) *reinterpret_cast<uint2*>(q + static_cast<size_t>(id) * 8) = quant16_e2m1(v, inv);
+    if (valid) *reinterpret_cast<uint2*>(q + id * 8) = quant16_e2m1(v, inv);
     // Scale bytes: four consecutive K-blocks of a row are four consecutive bytes of the tile
     // layout, so when the row length allows it one lane stores all four as a word.
     constexpr int LANES_PER_BLK = FMT == 0 ? 1 : 2;
@@ -334,6 +349,7 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __res
             *reinterpret_cast<uint32_t*>(sf + sfi(row, blk)) = word;
     } else if (valid && writer) {
         sf[sfi(row, blk)] = static_cast<uint8_t>(sfb);
+    }
     }
 }
 
@@ -373,10 +389,10 @@ static cudaError_t quant_fp8_typed(const T* x, long long rows, long long cols, i
         }
         quant_fp8_tensor_kernel<T><<<grid, 256, 0, st>>>(x, n, scale_given ? nullptr : ws, scale_io, q);
     } else if (mode == DSL_FP8_GROUP_1X128) {
-        const long long threads = rows * ((cols + 127) / 128) * 8;
-        const long long grid = (threads + 255) / 256;
-        if (grid > 0)
-            quant_fp8_1x128_kernel<T><<<static_cast<unsigned>(grid), 256, 0, st>>>(x, rows, static_cast<int>(cols), q, scale_io);
+        const RowMap rm = make_row_map(cols, 3);
+        const dim3 grid = row_map_grid(rm, rows, cols);
+        if (grid.x > 0 && grid.y > 0)
+            quant_fp8_1x128_kernel<T><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), q, scale_io, rm.log2_cp);
     } else {
         dim3 grid(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>((rows + 127) / 128));
         if (grid.x > 0 && grid.y > 0)
@@ -410,13 +426,15 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
         amax_kernel<T><<<grid_for(n / 16, 256, 148 * 16), 256, 0, st>>>(x, n, ws);
         nvfp4_global_scale_kernel<<<1, 1, 0, st>>>(ws, gs_io);
     }
-    const long long chunks = rows * (cols / 16);
-    const long long grid = (chunks + 255) / 256;
-    if (grid > 0) {
+    const RowMap rm = make_row_map(cols, 1);
+    dim3 grid = row_map_grid(rm, rows, cols);
+    const unsigned cap = 148u * 16u / (grid.y > 0 ? grid.y : 1u) + 1u;   // persistent: a few CTAs per SM
+    if (grid.x > cap) grid.x = cap;
+    if (grid.x > 0 && grid.y > 0) {
         if (format == DSL_FP4_NV)
-            quant_fp4_kernel<T, 0><<<static_cast<unsigned>(grid), 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, q, sf, group_offsets, num_groups);
+            quant_fp4_kernel<T, 0><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, q, sf, group_offsets, num_groups, rm.log2_cp);
         else
-            quant_fp4_kernel<T, 1><<<static_cast<unsigned>(grid), 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, q, sf, group_offsets, num_groups);
+            quant_fp4_kernel<T, 1><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, q, sf, group_offsets, num_groups, rm.log2_cp);
     }
     return cudaGetLastError();
 }
