@@ -353,6 +353,51 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __res
     }
 }
 
+
+// Small tensors (decode: a handful of activation rows): tensor amax, global scale and the NVFP4
+// quantisation in ONE launch of a single CTA, instead of memset + amax + scale + quantise.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+quant_nvfp4_small_kernel(const T* __restrict__ x, int M, int K, float* __restrict__ gs_out,
+                         uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+    __shared__ float red[32];
+    __shared__ float s_gs;
+    const int cpr = K / 16;
+    const int total = M * cpr;
+    float m = 0.f;
+    for (int c = threadIdx.x; c < total; c += blockDim.x) {
+        float v[16];
+        load16<T>(x + static_cast<size_t>(c) * 16, v);
+        m = fmaxf(m, amax16(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane_id() == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = 0.f;
+        for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) a = fmaxf(a, red[i]);
+        s_gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
+        *gs_out = s_gs;
+    }
+    __syncthreads();
+    const float gs = s_gs;
+    const int katoms = (cpr + 3) / 4;
+    for (int c = threadIdx.x; c < total; c += blockDim.x) {
+        const int row = c / cpr, kc = c - row * cpr;
+        float v[16];
+        load16<T>(x + static_cast<size_t>(c) * 16, v);   // second read comes from L1/L2
+        float t = __fdiv_rn(__fdiv_rn(amax16(v), 6.0f), gs);
+        t = fminf(t, 448.0f);
+        const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
+        const float d = __fmul_rn(e4m3_to_float(sfb), gs);
+        const float inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+        *reinterpret_cast<uint2*>(q + static_cast<size_t>(c) * 8) = quant16_e2m1(v, inv);
+        sf[(static_cast<size_t>(row >> 7) * katoms + (kc >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kc & 3)] =
+            static_cast<uint8_t>(sfb);
+    }
+}
+
 // ---- byte-matrix transpose ([R, C] -> [C, R]), used to turn a [K, N] weight K-major --------
 __global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out,
                                                            int R, int C) {
@@ -419,6 +464,10 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
     if (sf_needs_clear && sf_bytes > 0) {
         e = cudaMemsetAsync(sf, 0, sf_bytes, st);
         if (e != cudaSuccess) return e;
+    }
+    if (format == DSL_FP4_NV && !gs_given && group_offsets == nullptr && n <= (32u << 10)) {
+        quant_nvfp4_small_kernel<T><<<1, 1024, 0, st>>>(x, static_cast<int>(rows), static_cast<int>(cols), gs_io, q, sf);
+        return cudaGetLastError();
     }
     if (format == DSL_FP4_NV && !gs_given) {
         e = cudaMemsetAsync(ws, 0, 4, st);
