@@ -104,7 +104,7 @@ def make_moe_offsets(rng, tokens, experts, topk):
     return np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
 
 
-def build_workload(name, rank, world, device, sets):
+def build_workload(name, rank, world, device, sets, strong=False):
     """Returns dict(step=callable(i)->out, gemm=callable, flops, rows, desc...) with `sets`
     rotating copies of inputs so consecutive steps never reuse L2-resident operands."""
     from dsl_tool_b200 import pack_weight
@@ -114,13 +114,25 @@ def build_workload(name, rank, world, device, sets):
     g = torch.Generator(device=device).manual_seed(1234 + rank)
     offs = None
     if cfg.get("moe"):
-        experts = cfg["experts"]          # per rank: weak scaling keeps 64 local experts per GPU
-        offs_np = make_moe_offsets(np.random.default_rng(99 + rank), cfg["tokens"], experts, cfg["topk"])
+        experts = cfg["experts"]          # weak scaling keeps 64 local experts (and their routed rows) per GPU
+        if strong:                        # strong scaling: one global routing, this rank owns experts/world of them
+            from dsl_tool_b200.sharding import expert_ranges, local_rows
+            glob = make_moe_offsets(np.random.default_rng(99), cfg["tokens"], experts, cfg["topk"])
+            first, last = expert_ranges(experts, world)[rank]
+            _, _, loc = local_rows(glob, first, last)
+            offs_np = np.asarray(loc, dtype=np.int32)
+            experts = last - first
+        else:
+            offs_np = make_moe_offsets(np.random.default_rng(99 + rank), cfg["tokens"], experts, cfg["topk"])
         offs = torch.from_numpy(offs_np).to(device)
         M, K, N = int(offs_np[-1]), cfg["K"], cfg["N"]
         wshape = (experts, N, K)
     else:
         M, K, N = cfg["M"], cfg["K"], cfg["N"]
+        if strong:                        # this rank's 128-aligned column range of the one weight
+            from dsl_tool_b200.sharding import column_ranges
+            c0, c1 = column_ranges(N, world)[rank]
+            N = c1 - c0
         wshape = (1, N, K)
     acts, wts = [], []
     for s in range(sets):
@@ -241,6 +253,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sets", type=int, default=4, help="rotating input sets (keeps operands out of L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank holds a full-size shard (default); strong: the one problem is split "
+                         "across ranks (columns / experts)")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step (quantise + GEMM) from a CUDA graph: removes host launch gaps, "
                          "which dominate the decode-sized workloads")
@@ -264,7 +279,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     from dsl_tool_b200 import _lib
-    wl = build_workload(args.workload, rank, world, device, args.sets)
+    wl = build_workload(args.workload, rank, world, device, args.sets, strong=args.scaling == "strong")
     quant, gemm = split_step(wl)
     K_steps, W = args.steps, args.warmup
 
@@ -379,10 +394,11 @@ def main():
         hbm = None
     line = {
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": DTYPE_NAME[kind], "data": "synthetic",
         "config": {"workload": args.workload, "M": wl["M"], "K": wl["K"], "N": wl["N"], "out": "bf16",
-                   "moe": wl["moe"], "per_rank": "own weight shard / experts of this size, no collective",
+                   "moe": wl["moe"], "per_rank": ("own weight shard / experts of this size, no collective" if args.scaling == "weak" else
+                                "this rank's column range / experts of the one problem, no collective"),
                    "step": "activation quantise + GEMM, weights quantised once",
                    "l2": f"inputs rotate over {args.sets} sets (larger than the 126 MB L2)"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
