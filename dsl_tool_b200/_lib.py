@@ -66,6 +66,8 @@ _SIGNATURES = {
                           ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_gemm_fp4_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i,
                                          ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_quant_fp4_ref32": (_i, [_vp, _i, _ll, _vp, _vp, _vp]),
+    "dsl_gemm_fp4_ref32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),
 }

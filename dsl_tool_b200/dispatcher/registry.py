@@ -40,7 +40,7 @@ def _gemm_input_schema(kernel_name: str) -> dict:
         schema["scale_a"] = "Tensor uint8 (tiled block scales; packed operands only)"
         schema["scale_b"] = "Tensor uint8 (tiled block scales; packed operands only)"
         schema["use_mxfp4"] = "bool (default false)"
-        schema["format"] = "str: nvfp4 | mxfp4"
+        schema["format"] = "str: nvfp4 | mxfp4 | ref32 (the reference container: fp32 scale per 32)"
     if "grouped" in kernel_name:
         schema["num_groups"] = "int"
         schema["expert_offsets"] = "Tensor[G+1] int32 (ragged groups; optional)"

@@ -294,16 +294,19 @@ def fp4_gemm(A: torch.Tensor, B, scale_a: Optional[torch.Tensor] = None, scale_b
     `fp4_gemm(A, B, C, scale_a, scale_b, M, N, K, use_mxfp4)` (cuda/gemm/fp4_gemm.cu:140-146), with
     M, N, K read from the tensors and C returned.
 
-    format "nvfp4" (default; e2m1 + unsigned-E4M3 scale per 16 + fp32 global scale) or "mxfp4"
-    (`use_mxfp4=True`; e2m1 + E8M0 scale per 32).
+    format "nvfp4" (default; e2m1 + unsigned-E4M3 scale per 16 + fp32 global scale), "mxfp4"
+    (`use_mxfp4=True`; e2m1 + E8M0 scale per 32), or "ref32" - the reference's own container (fp32 scale
+    per 32, B packed [K, N/2]), computed bit-identically to its kernel.
     * High-precision A [M,K] and B ([K,N] for b_layout "kn", [N,K] for "nk"): quantised on the GPU.
     * Packed operands (uint8/int8, two e2m1 per byte, low nibble first): A [M,K/2], B K-major
       [N,K/2] (b_layout must be "nk"), `scale_a` / `scale_b` the tiled scale bytes, and for
       NVFP4 `global_scale_a` / `global_scale_b`.
     """
     fmt = format if format is not None else ("mxfp4" if use_mxfp4 else "nvfp4")
+    if fmt == "ref32":
+        return _fp4_gemm_ref32(A, B, scale_a, scale_b)
     if fmt not in ("nvfp4", "mxfp4"):
-        raise ValueError(f"format must be 'nvfp4' or 'mxfp4', got {fmt!r}")
+        raise ValueError(f"format must be 'nvfp4', 'mxfp4' or 'ref32', got {fmt!r}")
     if b_layout not in ("kn", "nk"):
         raise ValueError("b_layout must be 'kn' or 'nk'")
     _lib.require_cuda(A, B if isinstance(B, torch.Tensor) else None)
@@ -327,6 +330,33 @@ def fp4_gemm(A: torch.Tensor, B, scale_a: Optional[torch.Tensor] = None, scale_b
         raise ValueError(f"inner dimensions differ: A {tuple(A.shape)} vs B {tuple(B.shape)} ({b_layout})")
     w = pack_weight(B, fmt, layout=b_layout)
     return linear(A, w, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
+
+
+def _fp4_gemm_ref32(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor) -> torch.Tensor:
+    """The reference's own container and arithmetic (cuda/gemm/fp4_gemm.cu:95-146): A packed [M, K/2], B packed
+    [K, N/2] (pairs along N), scale_a [M, K/32] fp32, scale_b [K/32, N] fp32 -> fp32 [M, N], bit-identical to
+    the reference kernel.  `use_mxfp4` has no numeric effect there (its two tables are equal, fp4_gemm.cu:30-39)."""
+    dev = _lib.require_cuda(A, B, scale_a, scale_b)
+    if scale_a is None or scale_b is None:
+        raise ValueError("format 'ref32' takes packed operands with scale_a [M, K/32] and scale_b [K/32, N]")
+    if A.dtype not in _BYTE_DTYPES or B.dtype not in _BYTE_DTYPES or A.dim() != 2 or B.dim() != 2:
+        raise TypeError("format 'ref32' takes packed uint8 operands A [M, K/2] and B [K, N/2]")
+    M, K = A.shape[0], A.shape[1] * 2
+    N = B.shape[1] * 2
+    if B.shape[0] != K:
+        raise ValueError(f"inner dimensions differ: A {tuple(A.shape)} vs B {tuple(B.shape)}")
+    if K % 32 or N % 8:
+        raise ValueError("format 'ref32' needs K % 32 == 0 and N % 8 == 0")
+    sa = scale_a.to(torch.float32).contiguous()
+    sb = scale_b.to(torch.float32).contiguous()
+    if sa.numel() != M * (K // 32) or sb.numel() != (K // 32) * N:
+        raise ValueError("scale_a must hold M*K/32 and scale_b K/32*N fp32 values")
+    out = torch.empty((M, N), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_gemm_fp4_ref32(_bytes2d(A).data_ptr(), _bytes2d(B).data_ptr(), out.data_ptr(), sa.data_ptr(),
+                                           sb.data_ptr(), M, N, K, _lib.stream_ptr())
+    _lib.check(rc, "dsl_gemm_fp4_ref32")
+    return out
 
 
 def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_offsets: Optional[torch.Tensor] = None,

@@ -111,6 +111,21 @@ def quantize_fp4(x: torch.Tensor, format: str = "nvfp4",
     return q, sf, gs
 
 
+def quantize_fp4_ref32(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The reference's FP4 quantiser (`quantize_fp32_to_nvfp4`, cuda/gemm/fp4_gemm.cu:50-90) over the flat
+    buffer: (packed nibbles uint8 [ceil(n/2)], fp32 scale per 32 elements [ceil(n/32)])."""
+    dev = _lib.require_cuda(x)
+    x = x.contiguous()
+    n = x.numel()
+    q = torch.empty((n + 1) // 2, dtype=torch.uint8, device=dev)
+    s = torch.empty((n + 31) // 32, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_quant_fp4_ref32(x.data_ptr(), _lib.dtype_code(x.dtype), n, q.data_ptr(), s.data_ptr(),
+                                            _lib.stream_ptr())
+    _lib.check(rc, "dsl_quant_fp4_ref32")
+    return q, s
+
+
 def transpose_bytes(x: torch.Tensor) -> torch.Tensor:
     """[R, C] one-byte elements -> [C, R] (same dtype)."""
     dev = _lib.require_cuda(x)

@@ -141,6 +141,19 @@ int dsl_gemm_fp4(const uint8_t* A, const uint8_t* B, const uint8_t* sfa, const u
                  const dsl_epilogue* ep, uint32_t* status, void* stream);
 
 /*
+ * The reference's own FP4 container (its "NVFP4" and "MXFP4" are one format, cuda/gemm/fp4_gemm.cu:30-42):
+ * e2m1 nibbles with one fp32 scale per 32 contiguous elements of the FLAT buffer.
+ * dsl_quant_fp4_ref32 replaces quantize_fp32_to_nvfp4 (fp4_gemm.cu:50-90) bit for bit (scale = max(amax/6,
+ * 1e-12), ties to the lower table index): q_out ceil(n/2) bytes, scales_out ceil(n/32) floats.
+ * dsl_gemm_fp4_ref32 replaces fp4_gemm (fp4_gemm.cu:95-146) bit for bit: A packed [M,K] (pairs along K),
+ * B packed [K,N] (pairs along N), scale_a [M,K/32], scale_b [K/32,N], C fp32 [M,N].  K % 32 == 0, N % 8 == 0.
+ * Runs on the integer dot-product units (fp32 scales per 32 cannot ride in the block-scaled MMA).
+ */
+int dsl_quant_fp4_ref32(const void* x, int dtype, long long n, uint8_t* q_out, float* scales_out, void* stream);
+int dsl_gemm_fp4_ref32(const uint8_t* A, const uint8_t* B, float* C, const float* scale_a, const float* scale_b,
+                       int M, int N, int K, void* stream);
+
+/*
  * dsl_gemm_fp4 for callers that cannot allocate device memory (no counterpart in the
  * reference).  Same operands and result as dsl_gemm_fp4 on a dense problem, but the split-K
  * scratch is a fixed DSL_STATIC_SCRATCH_BYTES array inside the library instead of
