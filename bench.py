@@ -175,12 +175,12 @@ def split_step(wl):
         w = wl["wts"][i % sets]
         common = dict(n=w.n, out_dtype=torch.bfloat16, expert_offsets=offs)
         if kind == "fp8":
-            return GK.gemm_fp8_quantized(q[0], w.q, q[1], w.scale, **common)
+            return GK.gemm_fp8_quantized(q[0], w.q, q[1], w.scale, b_static=True, **common)
         if kind == "fp8_block128":
             return GK.gemm_fp8_groupwise_quantized(q[0], w.q, q[1], w.scale, sb_block=True, **common)
         if kind in ("nvfp4", "mxfp4"):
             return GK.gemm_fp4_quantized(q[0], w.q, q[1], w.scale, format=kind, global_scale_a=q[2],
-                                         global_scale_b=w.global_scale, **common)
+                                         global_scale_b=w.global_scale, b_static=True, **common)
         return GK.gemm_bf16_raw(q[0], w.q, **common)
 
     return quant, gemm
@@ -388,7 +388,7 @@ def main():
         step_bytes = (wl["M"] + wl["N"]) * wl["K"] * (0.5 + 1.0 / sfdiv) + 2.0 * wl["M"] * wl["N"] + 2.0 * wl["M"] * wl["K"]
         hbm = {"bound": "hbm", "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak, "traffic": None,
-               "kernel": "quantise + split-K gemm + reduce (whole step)", "bytes_per_step": step_bytes,
+               "kernel": "activation quantise + weight-streaming gemm (whole step)", "bytes_per_step": step_bytes,
                "peak_basis": f"{basis} HBM copy {hbm_peak} GB/s"}
     else:
         hbm = None
@@ -408,9 +408,11 @@ def main():
         "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": wl["M"] * wl["N"] * 2,
                 "ms_per_step": e2e_ms},
-        # kernels of this library per step: quantiser passes + GEMM (+ split-K reduction on decode shapes)
-        "gpu_launches": K_steps * ({"fp8": 3, "fp8_block128": 2, "nvfp4": 4, "mxfp4": 2, "bf16": 1}[kind]
-                                   + (1 if decode else 0)),
+        # kernels of this library per step: quantiser passes + one GEMM kernel (NVFP4 tensors of up to
+        # 2^18 elements are quantised by a single launch, larger ones by an amax pass + a quantise pass)
+        "gpu_launches": K_steps * ({"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
+                                    "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]
+                                   + (1 if (decode and wl["M"] > 32) else 0)),   # split-K reduction of the tiled kernel
         "cuda_graph": bool(args.graph),
         "clocks": clocks,
     }

@@ -45,6 +45,7 @@ class Epilogue(ctypes.Structure):
         ("out_dtype", ctypes.c_int),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
+        ("b_is_static", ctypes.c_int),
     ]
 
 

@@ -97,6 +97,7 @@ static int fill_common(GemmArgs& a, const void* A, const void* B, void* C, long 
     a.ldc = ldc;
     a.out_bf16 = ep->out_dtype == DSL_BF16;
     a.status = status;
+    a.b_static = ep->b_is_static != 0;
     if (ep->workspace != nullptr && aligned16(ep->workspace)) {
         a.partial = static_cast<float*>(ep->workspace);
         a.partial_bytes = ep->workspace_bytes;

@@ -415,12 +415,13 @@ static int launch_one(const void* A, const void* B, const GemmArgs& args, long l
 
 // Which kernel serves a problem: the CTA-pair kernel (256x256 tiles) once there is more than
 // one 128-row tile of work and the output is at least 256 wide; the 1-CTA kernel otherwise.
-// DSLGEMM_KERNEL=1cta|pair overrides the choice (for measurements).
+// Dense problems with at most DSL_DECODE_MAX_ROWS activation rows go to the weight-streaming kernel.
+// DSLGEMM_KERNEL=1cta|pair|decode overrides the choice (for measurements).
 static int forced_kernel() {
     static int v = []() {
         const char* e = getenv("DSLGEMM_KERNEL");
         if (e == nullptr) return 0;
-        return strcmp(e, "1cta") == 0 ? 1 : (strcmp(e, "pair") == 0 ? 2 : 0);
+        return strcmp(e, "1cta") == 0 ? 1 : (strcmp(e, "pair") == 0 ? 2 : (strcmp(e, "decode") == 0 ? 3 : 0));
     }();
     return v;
 }
@@ -442,6 +443,10 @@ int choose_split_k(const GemmArgs& args, long long tiles) {
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st) {
     if (args.m_total <= 0 || args.n <= 0) return 0;
     const int forced = forced_kernel();
+    if (forced == 0 || forced == 3) {
+        const int rc = launch_gemm_decode(kind, A, B, args, st);
+        if (rc != DSL_NOT_SERVED) return rc;
+    }
     if (forced == 2 || (forced == 0 && args.m_total > 128 && args.n >= 256)) return launch_gemm_pair(kind, A, B, args, st);
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
     // Narrow outputs get 128-wide tiles (two accumulator stages, more CTAs in flight).

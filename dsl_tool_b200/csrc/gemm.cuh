@@ -36,9 +36,14 @@ struct GemmArgs {
     int split_k;                 // > 1: K is cut into this many slices whose fp32 partial sums go to `partial`
     float* partial;              // [split_k, m_total, n] scratch (dense problems only)
     size_t partial_bytes;        // capacity of `partial`
+    int b_static;                // B was complete before the preceding kernel of the stream was launched
     uint32_t* status;
 };
 
+constexpr int DSL_DECODE_MAX_ROWS = 32;    // activation rows the weight-streaming kernel (gemm_decode.cu) takes
+constexpr int DSL_NOT_SERVED = -1000;      // launch_gemm_decode: problem outside its domain, use the tiled kernels
+
+int launch_gemm_decode(int kind, const void* A, const void* B, const GemmArgs& args, cudaStream_t st);
 int choose_split_k(const GemmArgs& args, long long tiles);
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);
 int launch_gemm_pair(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);

@@ -132,11 +132,6 @@ __global__ void __launch_bounds__(256) amax_kernel(const T* __restrict__ x, size
     if (lane_id() == 0 && m > 0.f) atomicMax(amax_bits, __float_as_uint(m));
 }
 
-__global__ void nvfp4_global_scale_kernel(const uint32_t* amax_bits, float* gs) {
-    float a = __uint_as_float(*amax_bits);
-    *gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
-}
-
 // Division-free thread -> (row, 16-element chunk) mapping shared by the row-wise quantisers.
 // A block of 256 threads covers `rows_per_block` rows x 2^log2_cp chunk slots (slots past the
 // row's real chunk count idle); rows longer than 256 chunks take several blocks along grid.y.
@@ -164,6 +159,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 quant_fp8_tensor_kernel(const T* __restrict__ x, size_t n, const uint32_t* amax_bits, float* scale_io,
                         uint8_t* __restrict__ q) {
+    griddep_launch_dependents();
     float s;
     if (amax_bits != nullptr) {
         s = fp8_scale_from_amax(__uint_as_float(*amax_bits));
@@ -273,9 +269,10 @@ struct SfIndexer {
 
 template <typename T, int FMT>   // FMT 0: NVFP4 (block 16, UE4M3 + global scale)  1: MXFP4 (block 32, E8M0)
 __global__ void __launch_bounds__(256)
-quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __restrict__ gs_ptr,
-                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
+quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict__ gs_ptr,
+                 const uint32_t* __restrict__ amax_bits, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
                  int num_groups, int log2_cp) {
+    griddep_launch_dependents();   // a GEMM that opted in may set itself up (and stream its weight) from now on
     __shared__ int s_offs[kMaxGroups + 1];
     __shared__ int s_tile0[kMaxGroups + 1];
     SfIndexer sfi;
@@ -299,6 +296,17 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __res
         sfi.offs = s_offs;
         sfi.tile0 = s_tile0;
     }
+    // NVFP4 global scale: given (gs_ptr holds it) or derived here from the tensor amax and published
+    float gs = 1.0f;
+    if (FMT == 0) {
+        if (amax_bits != nullptr) {
+            const float a = __uint_as_float(*amax_bits);
+            gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
+            if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *gs_ptr = gs;
+        } else {
+            gs = *gs_ptr;
+        }
+    }
     const int cpr = K / 16;   // 16-element chunks per row
     const int rpb = 256 >> log2_cp;
     const long long row_blocks = (M + rpb - 1) / rpb;
@@ -318,7 +326,6 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, const float* __res
     int blk;
     bool writer;
     if (FMT == 0) {
-        const float gs = *gs_ptr;
         float t = __fdiv_rn(__fdiv_rn(m, 6.0f), gs);
         t = fminf(t, 448.0f);
         sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
@@ -360,6 +367,7 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 quant_nvfp4_small_kernel(const T* __restrict__ x, int M, int K, float* __restrict__ gs_out,
                          uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+    griddep_launch_dependents();
     __shared__ float red[32];
     __shared__ float s_gs;
     const int cpr = K / 16;
@@ -396,6 +404,80 @@ quant_nvfp4_small_kernel(const T* __restrict__ x, int M, int K, float* __restric
         sf[(static_cast<size_t>(row >> 7) * katoms + (kc >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kc & 3)] =
             static_cast<uint8_t>(sfb);
     }
+}
+
+// Up to 256 K elements (decode batches): the same single launch, spread over
+// one cluster of eight CTAs.  Each CTA reduces its share, the eight maxima meet through
+// distributed shared memory at a cluster barrier, and every CTA then quantises its share (second
+// read from L1/L2).  The padding bytes of the scale tiles are zeroed here too, so this path
+// needs no memset and no scratch word.
+constexpr int kQuantClusterCtas = 8;
+__device__ __forceinline__ float ld_cluster_f32(const float* local_ptr, uint32_t rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_ptr)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+template <typename T>
+__global__ void __cluster_dims__(kQuantClusterCtas, 1, 1) __launch_bounds__(1024)
+quant_nvfp4_cluster_kernel(const T* __restrict__ x, int M, int K, float* __restrict__ gs_out,
+                           uint8_t* __restrict__ q, uint8_t* __restrict__ sf, unsigned sf_clear_vec16) {
+    griddep_launch_dependents();
+    __shared__ float red[32];
+    __shared__ float s_cta_amax;
+    __shared__ float s_gs;
+    const uint32_t rank = cluster_ctarank();
+    const int gtid = static_cast<int>(rank) * 1024 + threadIdx.x;
+    constexpr int kThreads = kQuantClusterCtas * 1024;
+    for (unsigned i = gtid; i < sf_clear_vec16; i += kThreads) reinterpret_cast<uint4*>(sf)[i] = make_uint4(0u, 0u, 0u, 0u);
+    const int cpr = K / 16;
+    const int total = M * cpr;
+    float m = 0.f;
+    for (int c = gtid; c < total; c += kThreads) {
+        float v[16];
+        load16<T>(x + static_cast<size_t>(c) * 16, v);
+        m = fmaxf(m, amax16(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane_id() == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float a = red[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        if (threadIdx.x == 0) s_cta_amax = a;
+    }
+    cluster_sync_all();     // maxima published; the zeroed scale bytes are ordered before any scale store below
+    if (threadIdx.x < 32) {
+        float a = threadIdx.x < kQuantClusterCtas ? ld_cluster_f32(&s_cta_amax, threadIdx.x) : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        if (threadIdx.x == 0) {
+            s_gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
+            if (rank == 0) *gs_out = s_gs;
+        }
+    }
+    __syncthreads();
+    // this CTA is done reading its peers; they may not exit before everyone has said so (waited for at the end)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    const float gs = s_gs;
+    const int katoms = (cpr + 3) / 4;
+    for (int c = gtid; c < total; c += kThreads) {
+        const int row = c / cpr, kc = c - row * cpr;
+        float v[16];
+        load16<T>(x + static_cast<size_t>(c) * 16, v);
+        float t = __fdiv_rn(__fdiv_rn(amax16(v), 6.0f), gs);
+        t = fminf(t, 448.0f);
+        const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
+        const float d = __fmul_rn(e4m3_to_float(sfb), gs);
+        const float inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+        *reinterpret_cast<uint2*>(q + static_cast<size_t>(c) * 8) = quant16_e2m1(v, inv);
+        sf[(static_cast<size_t>(row >> 7) * katoms + (kc >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kc & 3)] =
+            static_cast<uint8_t>(sfb);
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ---- byte-matrix transpose ([R, C] -> [C, R]), used to turn a [K, N] weight K-major --------
@@ -461,6 +543,11 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
                                    const int* group_offsets, int num_groups, uint32_t* ws, cudaStream_t st) {
     const size_t n = static_cast<size_t>(rows) * cols;
     cudaError_t e;
+    if (format == DSL_FP4_NV && !gs_given && group_offsets == nullptr && n > (32u << 10) && n <= (256u << 10)) {
+        const unsigned clear16 = sf_needs_clear ? static_cast<unsigned>(sf_bytes / 16) : 0u;
+        quant_nvfp4_cluster_kernel<T><<<kQuantClusterCtas, 1024, 0, st>>>(x, static_cast<int>(rows), static_cast<int>(cols), gs_io, q, sf, clear16);
+        return cudaGetLastError();
+    }
     if (sf_needs_clear && sf_bytes > 0) {
         e = cudaMemsetAsync(sf, 0, sf_bytes, st);
         if (e != cudaSuccess) return e;
@@ -473,17 +560,17 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
         e = cudaMemsetAsync(ws, 0, 4, st);
         if (e != cudaSuccess) return e;
         amax_kernel<T><<<grid_for(n / 16, 256, 148 * 16), 256, 0, st>>>(x, n, ws);
-        nvfp4_global_scale_kernel<<<1, 1, 0, st>>>(ws, gs_io);
     }
+    const uint32_t* amax_bits = (format == DSL_FP4_NV && !gs_given) ? ws : nullptr;
     const RowMap rm = make_row_map(cols, 1);
     dim3 grid = row_map_grid(rm, rows, cols);
     const unsigned cap = 148u * 16u / (grid.y > 0 ? grid.y : 1u) + 1u;   // persistent: a few CTAs per SM
     if (grid.x > cap) grid.x = cap;
     if (grid.x > 0 && grid.y > 0) {
         if (format == DSL_FP4_NV)
-            quant_fp4_kernel<T, 0><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, q, sf, group_offsets, num_groups, rm.log2_cp);
+            quant_fp4_kernel<T, 0><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, amax_bits, q, sf, group_offsets, num_groups, rm.log2_cp);
         else
-            quant_fp4_kernel<T, 1><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, q, sf, group_offsets, num_groups, rm.log2_cp);
+            quant_fp4_kernel<T, 1><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, nullptr, q, sf, group_offsets, num_groups, rm.log2_cp);
     }
     return cudaGetLastError();
 }

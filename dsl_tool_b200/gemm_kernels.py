@@ -36,8 +36,10 @@ def _out_dtype(name) -> torch.dtype:
 
 
 def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
-              row_scale: Optional[torch.Tensor], col_scale: Optional[torch.Tensor], keep: list) -> _lib.Epilogue:
+              row_scale: Optional[torch.Tensor], col_scale: Optional[torch.Tensor], keep: list,
+              b_static: bool = False) -> _lib.Epilogue:
     ep = _lib.Epilogue()
+    ep.b_is_static = 1 if b_static else 0
     for name, s in (("a", scale_a), ("b", scale_b)):
         host, devp = 1.0, None
         if isinstance(s, torch.Tensor):
@@ -85,8 +87,10 @@ def _offsets_arg(offsets: Optional[torch.Tensor], dev) -> Tuple[Optional[torch.T
 
 def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, scale_b: Scalar, *, n: int,
                        out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
-                       row_scale=None, col_scale=None) -> torch.Tensor:
-    """C = (qa @ qb^T) * scale_a * scale_b on E4M3 bytes; qa [M, K], qb_nk [G*N, K]."""
+                       row_scale=None, col_scale=None, b_static: bool = False) -> torch.Tensor:
+    """C = (qa @ qb^T) * scale_a * scale_b on E4M3 bytes; qa [M, K], qb_nk [G*N, K].
+    `b_static`: the weight was complete before the previous kernel on this stream was launched
+    (lets the decode kernel stream it while the activation quantiser still runs)."""
     dev = _lib.require_cuda(qa, qb_nk)
     qa, qb_nk = _bytes2d(qa), _bytes2d(qb_nk)
     M, K = qa.shape
@@ -95,7 +99,7 @@ def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, s
         raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major bytes, got {tuple(qb_nk.shape)}")
     out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, scale_a, scale_b, out.dtype, row_scale, col_scale, keep)
+    ep = _epilogue(dev, scale_a, scale_b, out.dtype, row_scale, col_scale, keep, b_static)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_fp8(qa.data_ptr(), qb_nk.data_ptr(), out.data_ptr(), n, M, n, K, _lib.ptr(offs),
                                      groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
@@ -139,9 +143,10 @@ def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torc
 def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, *,
                        format: str, n: int, global_scale_a: Scalar = None, global_scale_b: Scalar = None,
                        out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
-                       row_scale=None, col_scale=None) -> torch.Tensor:
+                       row_scale=None, col_scale=None, b_static: bool = False) -> torch.Tensor:
     """Block-scaled FP4 GEMM on packed e2m1 operands pa [M, K/2], pb_nk [G*N, K/2] with tiled
-    scale bytes; for NVFP4 the result is multiplied once by global_scale_a * global_scale_b."""
+    scale bytes; for NVFP4 the result is multiplied once by global_scale_a * global_scale_b.
+    `b_static` as in gemm_fp8_quantized."""
     dev = _lib.require_cuda(pa, pb_nk, sfa, sfb)
     pa, pb_nk = _bytes2d(pa), _bytes2d(pb_nk)
     M, kb2 = pa.shape
@@ -159,7 +164,7 @@ def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor,
         raise ValueError("scale buffers are smaller than the tiled layout needs")
     out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, global_scale_a, global_scale_b, out.dtype, row_scale, col_scale, keep)
+    ep = _epilogue(dev, global_scale_a, global_scale_b, out.dtype, row_scale, col_scale, keep, b_static)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_fp4(pa.data_ptr(), pb_nk.data_ptr(), _bytes2d(sfa).data_ptr(),
                                      _bytes2d(sfb).data_ptr(), fmt, out.data_ptr(), n, M, n, K, _lib.ptr(offs),
@@ -195,7 +200,8 @@ def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torc
 def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
            expert_offsets: Optional[torch.Tensor] = None, row_scale=None, col_scale=None) -> torch.Tensor:
     """a [M, K] high-precision activations x packed weight -> [M, N]: quantise the activations
-    in the weight's format (one pass on the GPU) and run the matching GEMM."""
+    in the weight's format (one pass on the GPU) and run the matching GEMM.  The packed weight is
+    treated as complete (the activation quantiser always sits between its producer and the GEMM)."""
     if a.dim() != 2 or a.shape[1] != w.k:
         raise ValueError(f"activations must be [M, {w.k}], got {tuple(a.shape)}")
     if w.groups > 1 and expert_offsets is None:
@@ -205,7 +211,7 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
         return gemm_bf16_raw(a, w.q, **common)
     if w.format == "fp8":
         qa, sa = quantize_fp8(a, "per_tensor")
-        return gemm_fp8_quantized(qa, w.q, sa, w.scale, row_scale=row_scale, col_scale=col_scale, **common)
+        return gemm_fp8_quantized(qa, w.q, sa, w.scale, row_scale=row_scale, col_scale=col_scale, b_static=True, **common)
     if w.format == "fp8_block128":
         qa, sa = quantize_fp8(a, "groupwise")
         return gemm_fp8_groupwise_quantized(qa, w.q, sa, w.scale, sb_block=True, row_scale=row_scale,
@@ -213,7 +219,8 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
     if w.format in ("nvfp4", "mxfp4"):
         pa, sfa, gsa = quantize_fp4(a, w.format, group_offsets=expert_offsets)
         return gemm_fp4_quantized(pa, w.q, sfa, w.scale, format=w.format, global_scale_a=gsa,
-                                  global_scale_b=w.global_scale, row_scale=row_scale, col_scale=col_scale, **common)
+                                  global_scale_b=w.global_scale, row_scale=row_scale, col_scale=col_scale, b_static=True,
+                                  **common)
     raise ValueError(f"unknown packed-weight format {w.format!r}")
 
 

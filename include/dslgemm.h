@@ -86,8 +86,9 @@ int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream
 /* Epilogue description shared by the GEMM entry points.
  *   out = acc * scale_a * scale_b [* row_scale[m]] [* col_scale[g*N+n]]
  * scale_x is *scale_x_dev when that pointer is non-NULL, else scale_x_host.
- * With a workspace, dense problems that would occupy less than half of the SMs are cut along K
- * into up to 8 slices (each SM streams part of the weight) and summed in slice order. */
+ * With a workspace, dense problems with at most 128 rows go to the weight-streaming kernel (all SMs
+ * stream equal shares of B; shared tiles are summed in ascending K order), and other dense problems
+ * that would occupy less than half of the SMs are cut along K into up to 8 slices summed in order. */
 typedef struct {
     float scale_a_host, scale_b_host;
     const float* scale_a_dev;
@@ -97,6 +98,11 @@ typedef struct {
     int out_dtype;              /* DSL_F32 or DSL_BF16 */
     void* workspace;            /* optional scratch (16-byte aligned) for split-K partial sums, or NULL */
     size_t workspace_bytes;     /* its size; decode shapes (few rows, long K) use up to 8*M*N*4 bytes */
+    int b_is_static;            /* non-zero: B and its scale bytes were complete before the kernel that precedes
+                                   this call in the stream was launched (a pre-packed weight).  The weight-streaming
+                                   kernel is launched with programmatic stream serialisation and then starts
+                                   fetching B while that predecessor (e.g. the activation quantiser) still runs;
+                                   A, its scales and every output are touched only after the predecessor is done. */
 } dsl_epilogue;
 
 /*
