@@ -5,7 +5,11 @@
 Tensor wire format: {"shape": [...], "dtype": "...", "data": "<base64 little-endian bytes>"} or
 {"shape", "dtype", "fill": "zeros" | "ones" | "random" | <number>}.  bfloat16 travels as fp32
 bytes in both directions (a quirk of the reference kept on purpose, dispatcher.py:88-95,120-128).
-Beyond the reference's dtype names, "uint8" is accepted so packed FP4 / scale bytes can be sent.
+Beyond the reference's dtype names, "uint8", "float8_e8m0fnu" ("e8m0") and "float4_e2m1fn_x2"
+("fp4x2") are accepted so packed FP4 values and scale bytes can be sent (one byte per element on the
+wire), and a spec {"packed_file": "<path>"} stands for a weight written by `save_packed`: it
+deserialises to the PackedWeight (read once per process and device), so repeated calls neither ship
+nor requantise the weight.
 """
 from __future__ import annotations
 
@@ -27,11 +31,14 @@ _DTYPES: Dict[str, torch.dtype] = {
     "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
     "float8_e4m3fn": torch.float8_e4m3fn, "fp8": torch.float8_e4m3fn,
     "int8": torch.int8, "uint8": torch.uint8, "int32": torch.int32, "int64": torch.int64,
+    "float8_e8m0fnu": torch.float8_e8m0fnu, "e8m0": torch.float8_e8m0fnu,
+    "float4_e2m1fn_x2": torch.float4_e2m1fn_x2, "fp4x2": torch.float4_e2m1fn_x2,
 }
+_BYTE_VIEW = (torch.float8_e4m3fn, torch.float8_e8m0fnu, torch.float4_e2m1fn_x2)     # travel as their raw bytes
 # numpy view used for the raw bytes of each dtype on the wire
 _WIRE_NP = {torch.float32: np.float32, torch.float16: np.float16, torch.bfloat16: np.float32,
             torch.int8: np.int8, torch.uint8: np.uint8, torch.int32: np.int32, torch.int64: np.int64,
-            torch.float8_e4m3fn: np.uint8}
+            torch.float8_e4m3fn: np.uint8, torch.float8_e8m0fnu: np.uint8, torch.float4_e2m1fn_x2: np.uint8}
 
 
 def _resolve_dtype(name: str) -> torch.dtype:
@@ -41,7 +48,10 @@ def _resolve_dtype(name: str) -> torch.dtype:
         raise ValueError(f"Unknown dtype '{name}'. Supported: {list(_DTYPES)}") from None
 
 
-def deserialize_tensor(spec: Dict[str, Any], device: str = "cuda") -> torch.Tensor:
+def deserialize_tensor(spec: Dict[str, Any], device: str = "cuda"):
+    if "packed_file" in spec:
+        from ..weight_store import load_packed_cached
+        return load_packed_cached(spec["packed_file"], device)
     shape = tuple(spec["shape"])
     dtype = _resolve_dtype(spec.get("dtype", "bfloat16"))
     if "data" in spec:
@@ -50,10 +60,16 @@ def deserialize_tensor(spec: Dict[str, Any], device: str = "cuda") -> torch.Tens
         t = torch.from_numpy(arr)
         if dtype == torch.bfloat16:
             t = t.to(torch.bfloat16)
-        elif dtype == torch.float8_e4m3fn:
-            t = t.view(torch.float8_e4m3fn)
+        elif dtype in _BYTE_VIEW:
+            t = t.view(dtype)
         return t.to(device)
     fill = spec.get("fill", "random")
+    if dtype in _BYTE_VIEW and dtype != torch.float8_e4m3fn:      # packed / exponent-only bytes: only byte fills make sense
+        if fill == "zeros":
+            return torch.zeros(shape, dtype=torch.uint8, device=device).view(dtype)
+        if fill == "random":
+            return torch.randint(0, 127, shape, dtype=torch.uint8, device=device).view(dtype)
+        raise ValueError(f"fill {fill!r} is not defined for {dtype}; send data, or fill 'zeros' / 'random'")
     if fill == "zeros":
         return torch.zeros(shape, dtype=dtype, device=device)
     if fill == "ones":
@@ -71,7 +87,7 @@ def serialize_tensor(t: torch.Tensor) -> Dict[str, Any]:
     host = t.detach().cpu()
     if host.dtype == torch.bfloat16:
         host = host.to(torch.float32)
-    elif host.dtype == torch.float8_e4m3fn:
+    elif host.dtype in _BYTE_VIEW:
         host = host.view(torch.uint8)
     payload = base64.b64encode(host.contiguous().numpy().tobytes()).decode()
     return {"shape": list(t.shape), "dtype": str(t.dtype).replace("torch.", ""), "data": payload}

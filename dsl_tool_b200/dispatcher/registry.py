@@ -48,6 +48,8 @@ def _gemm_input_schema(kernel_name: str) -> dict:
     if "bf16" not in kernel_name:
         schema["b_layout"] = "str: kn | nk (default kn)"
         schema["out_dtype"] = "str: float32 | bfloat16"
+        schema["B (alternative)"] = '{"packed_file": path}: a weight written by save_packed, used in place of the tensor spec of B'
+        schema["cache_weights"] = "bool (default false): keep B's quantised form, keyed by tensor identity"
     return schema
 
 

@@ -18,9 +18,10 @@ import torch
 
 from . import _lib
 from .quantize import PackedWeight, pack_weight, quantize_fp4, quantize_fp8, transpose_bytes
+from .weight_store import cached_pack
 
 _FLOAT_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
-_BYTE_DTYPES = (torch.uint8, torch.int8, torch.float8_e4m3fn)
+_BYTE_DTYPES = (torch.uint8, torch.int8, torch.float8_e4m3fn, torch.float8_e8m0fnu, torch.float4_e2m1fn_x2)
 _OUT_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
 
 Scalar = Union[None, float, torch.Tensor]
@@ -230,7 +231,8 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
 
 def fp8_gemm(A: torch.Tensor, B, scale_a: Scalar = None, scale_b: Scalar = None, *, mode: str = "per_tensor",
              group_size: int = 128, b_layout: str = "kn", out_dtype="float32",
-             row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+             row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None,
+             cache_weights: bool = False) -> torch.Tensor:
     """FP8 E4M3 GEMM, C[M,N] = A[M,K] @ B[K,N] (triton/gemm/gemm_kernels.py:104-122).
 
     * A and B already E4M3 (float8_e4m3fn / uint8 / int8 bytes): `scale_a`, `scale_b` are the
@@ -242,7 +244,9 @@ def fp8_gemm(A: torch.Tensor, B, scale_a: Scalar = None, scale_b: Scalar = None,
       scale_b is used instead of the amax-derived one), or, for "groupwise"/"block128", with
       1x128 activation groups and 128x128 weight blocks.
     b_layout "kn" is the reference's B[K,N]; "nk" is a K-major weight [N,K] (no transpose
-    needed).  B may also be a PackedWeight.
+    needed).  B may also be a PackedWeight.  `cache_weights=True` keeps the quantised form of a
+    high-precision B in the process-wide identity cache (weight_store.cached_pack), so the next call
+    with the same, unmodified tensor skips its quantisation.
     """
     if mode not in ("per_tensor", "groupwise", "block128"):
         raise ValueError(f"mode must be per_tensor, groupwise or block128, got {mode!r}")
@@ -282,6 +286,13 @@ def fp8_gemm(A: torch.Tensor, B, scale_a: Scalar = None, scale_b: Scalar = None,
                                             out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
     if A.dtype not in _FLOAT_DTYPES or B.dtype not in _FLOAT_DTYPES:
         raise TypeError(f"unsupported dtypes {A.dtype}, {B.dtype}")
+    if cache_weights and scale_b is None:
+        w = cached_pack(B, "fp8" if mode == "per_tensor" else "fp8_block128", b_layout)
+        if mode == "per_tensor" and scale_a is not None:
+            qa, sa = quantize_fp8(A, "per_tensor", scale=scale_a)
+            return gemm_fp8_quantized(qa, w.q, sa, w.scale, n=N, out_dtype=out_dtype, row_scale=row_scale,
+                                      col_scale=col_scale, b_static=True)
+        return linear(A, w, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
     Bnk = B.t().contiguous() if b_layout == "kn" else B.contiguous()
     if mode == "per_tensor":
         qa, sa = quantize_fp8(A, "per_tensor", scale=scale_a)
@@ -296,7 +307,8 @@ def fp8_gemm(A: torch.Tensor, B, scale_a: Scalar = None, scale_b: Scalar = None,
 def fp4_gemm(A: torch.Tensor, B, scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
              use_mxfp4: bool = False, *, format: Optional[str] = None, b_layout: str = "kn",
              global_scale_a: Scalar = None, global_scale_b: Scalar = None, out_dtype="float32",
-             row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+             row_scale: Optional[torch.Tensor] = None, col_scale: Optional[torch.Tensor] = None,
+             cache_weights: bool = False) -> torch.Tensor:
     """Block-scaled FP4 GEMM; argument order of the reference host wrapper
     `fp4_gemm(A, B, C, scale_a, scale_b, M, N, K, use_mxfp4)` (cuda/gemm/fp4_gemm.cu:140-146), with
     M, N, K read from the tensors and C returned.
@@ -308,6 +320,7 @@ def fp4_gemm(A: torch.Tensor, B, scale_a: Optional[torch.Tensor] = None, scale_b
     * Packed operands (uint8/int8, two e2m1 per byte, low nibble first): A [M,K/2], B K-major
       [N,K/2] (b_layout must be "nk"), `scale_a` / `scale_b` the tiled scale bytes, and for
       NVFP4 `global_scale_a` / `global_scale_b`.
+    `cache_weights` as in fp8_gemm.
     """
     fmt = format if format is not None else ("mxfp4" if use_mxfp4 else "nvfp4")
     if fmt == "ref32":
@@ -335,7 +348,7 @@ def fp4_gemm(A: torch.Tensor, B, scale_a: Optional[torch.Tensor] = None, scale_b
         raise TypeError(f"unsupported dtypes {A.dtype}, {B.dtype}")
     if (B.shape[0] if b_layout == "kn" else B.shape[1]) != A.shape[1]:
         raise ValueError(f"inner dimensions differ: A {tuple(A.shape)} vs B {tuple(B.shape)} ({b_layout})")
-    w = pack_weight(B, fmt, layout=b_layout)
+    w = cached_pack(B, fmt, b_layout) if cache_weights else pack_weight(B, fmt, layout=b_layout)
     return linear(A, w, out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
 
 
@@ -367,7 +380,7 @@ def _fp4_gemm_ref32(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, sca
 
 
 def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_offsets: Optional[torch.Tensor] = None,
-                 *, format: str = "bf16", b_layout: str = "kn", out_dtype=None) -> torch.Tensor:
+                 *, format: str = "bf16", b_layout: str = "kn", out_dtype=None, cache_weights: bool = False) -> torch.Tensor:
     """Grouped GEMM for MoE / LoRA (triton/gemm/gemm_kernels.py:164-182, tilelang/gemm/gemm_kernels.py:116-133).
 
     Fixed-size groups: A [G,M,K], B [G,K,N] -> [G,M,N] (the reference's form; `num_groups`
@@ -377,6 +390,7 @@ def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_of
     format "bf16" multiplies unquantised (result in A.dtype, as the Triton reference); "fp8",
     "fp8_groupwise", "nvfp4", "mxfp4" quantise A and B on the GPU first (result fp32 unless
     out_dtype says otherwise).  B may be a PackedWeight.  b_layout "kn": B [G,K,N]; "nk": [G,N,K].
+    `cache_weights` as in fp8_gemm.
     """
     formats = {"bf16": "bf16", "fp8": "fp8", "fp8_groupwise": "fp8_block128", "nvfp4": "nvfp4", "mxfp4": "mxfp4"}
     if format not in formats:
@@ -392,7 +406,7 @@ def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_of
     else:
         if B.dim() != 3:
             raise ValueError(f"B must be 3-D, got {tuple(B.shape)}")
-        w = pack_weight(B, formats[format], layout=b_layout)
+        w = cached_pack(B, formats[format], b_layout) if cache_weights else pack_weight(B, formats[format], layout=b_layout)
     G = w.groups
     if num_groups is not None and int(num_groups) != G:
         raise ValueError(f"num_groups={num_groups} but B holds {G} groups")
