@@ -51,7 +51,8 @@ WORKLOADS = {
 DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
 # dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from an ncu capture of the
 # full-size workload (profiles/): bytes.  None where no capture exists.
-NCU_TRAFFIC = {"fp8_groupwise_llama8b_mlp": 77.1e6 + 74.9e6}
+NCU_TRAFFIC = {"fp8_groupwise_llama8b_mlp": 77.1e6 + 74.9e6,
+               "nvfp4_m16": 37.93e6 + 0.28e6}      # decode: GEMM + quantiser launch (whole step)
 PEAK_MULT = {"fp8": 2.0, "fp8_block128": 2.0, "nvfp4": 4.0, "mxfp4": 4.0, "bf16": 1.0}
 
 
@@ -387,7 +388,7 @@ def main():
         sfdiv = 16 if kind == "nvfp4" else 32
         step_bytes = (wl["M"] + wl["N"]) * wl["K"] * (0.5 + 1.0 / sfdiv) + 2.0 * wl["M"] * wl["N"] + 2.0 * wl["M"] * wl["K"]
         hbm = {"bound": "hbm", "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
-               "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+               "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak, "traffic": NCU_TRAFFIC.get(args.workload),
                "kernel": "activation quantise + weight-streaming gemm (whole step)", "bytes_per_step": step_bytes,
                "peak_basis": f"{basis} HBM copy {hbm_peak} GB/s"}
     else:
