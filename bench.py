@@ -46,6 +46,9 @@ WORKLOADS = {
     "mxfp4_llama70b_down": dict(kind="mxfp4", M=8192, K=28672, N=8192, wstd=0.015, outliers=False),
     "moe_nvfp4": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
     "moe_fp8_groupwise": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
+    "moe_nvfp4_swiglu": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02, act="swiglu"),
+    "moe_fp8_groupwise_swiglu": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
+                                     act="swiglu"),
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
 }
 DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
@@ -145,15 +148,16 @@ def build_workload(name, rank, world, device, sets, strong=False):
         acts.append(a.to(torch.bfloat16))
         del a
         w = (torch.randn(wshape, generator=g, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
-        wts.append(pack_weight(w, kind, layout="nk"))
+        wts.append(pack_weight(w, kind, layout="nk", gate_up_interleave=cfg.get("act") == "swiglu"))
         del w
     torch.cuda.synchronize()
 
     def step(i, a=None):
-        return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype=torch.bfloat16, expert_offsets=offs)
+        return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype=torch.bfloat16, expert_offsets=offs,
+                      activation=cfg.get("act"))
 
     return dict(step=step, acts=acts, wts=wts, offs=offs, M=M, K=K, N=N, kind=kind, flops=2.0 * M * N * K,
-                moe=bool(cfg.get("moe")))
+                moe=bool(cfg.get("moe")), act=cfg.get("act"))
 
 
 def split_step(wl):
@@ -174,7 +178,7 @@ def split_step(wl):
 
     def gemm(i, q):
         w = wl["wts"][i % sets]
-        common = dict(n=w.n, out_dtype=torch.bfloat16, expert_offsets=offs)
+        common = dict(n=w.n, out_dtype=torch.bfloat16, expert_offsets=offs, activation=wl.get("act"))
         if kind == "fp8":
             return GK.gemm_fp8_quantized(q[0], w.q, q[1], w.scale, b_static=True, **common)
         if kind == "fp8_block128":
@@ -345,7 +349,8 @@ def main():
     for j, h in enumerate(host_a):
         h.copy_(wl["acts"][j % len(wl["acts"])])
     dev_a = torch.empty_like(wl["acts"][0])
-    host_out = torch.empty((wl["M"], wl["N"]), dtype=torch.bfloat16).pin_memory()
+    out_cols = wl["N"] // 2 if wl.get("act") else wl["N"]
+    host_out = torch.empty((wl["M"], out_cols), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(K_steps, 10))
     for i in range(2):
         dev_a.copy_(host_a[i % 2], non_blocking=True)
@@ -397,7 +402,8 @@ def main():
         "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": DTYPE_NAME[kind], "data": "synthetic",
-        "config": {"workload": args.workload, "M": wl["M"], "K": wl["K"], "N": wl["N"], "out": "bf16",
+        "config": {"workload": args.workload, "M": wl["M"], "K": wl["K"], "N": wl["N"],
+                   "out": "bf16" if not wl.get("act") else "bf16 [M, N/2] = silu(gate) * up, folded in the GEMM epilogue",
                    "moe": wl["moe"], "per_rank": ("own weight shard / experts of this size, no collective" if args.scaling == "weak" else
                                 "this rank's column range / experts of the one problem, no collective"),
                    "step": "activation quantise + GEMM, weights quantised once",
@@ -407,7 +413,7 @@ def main():
                      "kernel": "gemm", "kernel_ms": gemm_ms, "quant_kernel_ms": quant_ms,
                      "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"},
         "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": wl["M"] * wl["N"] * 2,
+                "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": wl["M"] * out_cols * 2,
                 "ms_per_step": e2e_ms},
         # kernels of this library per step: quantiser passes + one GEMM kernel (NVFP4 tensors of up to
         # 2^18 elements are quantised by a single launch, larger ones by an amax pass + a quantise pass)

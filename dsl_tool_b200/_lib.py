@@ -19,6 +19,7 @@ LIB_PATH = os.environ.get("DSLGEMM_LIBRARY", os.path.join(_HERE, "libdslgemm.so"
 F32, BF16, F16 = 0, 1, 2
 FP8_PER_TENSOR, FP8_GROUP_1X128, FP8_BLOCK_128X128 = 0, 1, 2
 FP4_NV, FP4_MX = 0, 1
+ACT_NONE, ACT_SWIGLU = 0, 1
 MAX_GROUPS = 1024
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -46,6 +47,7 @@ class Epilogue(ctypes.Structure):
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("b_is_static", ctypes.c_int),
+        ("activation", ctypes.c_int),
     ]
 
 

@@ -76,7 +76,10 @@ static int fill_common(GemmArgs& a, const void* A, const void* B, void* C, long 
                        long long k_bytes, const int* group_offsets, int groups, const dsl_epilogue* ep,
                        uint32_t* status) {
     if (A == nullptr || B == nullptr || C == nullptr || ep == nullptr) return DSL_ERR_NULL;
-    if (M_total < 0 || N < 0 || k_bytes <= 0 || M_total > 0x7FFFFFFFll || ldc < N) return DSL_ERR_SHAPE;
+    if (ep->activation != DSL_ACT_NONE && ep->activation != DSL_ACT_SWIGLU) return DSL_ERR_ENUM;
+    const bool glu = ep->activation == DSL_ACT_SWIGLU;
+    if (glu && N % 2 != 0) return DSL_ERR_SHAPE;
+    if (M_total < 0 || N < 0 || k_bytes <= 0 || M_total > 0x7FFFFFFFll || ldc < (glu ? N / 2 : N)) return DSL_ERR_SHAPE;
     if (k_bytes % 16 != 0) return DSL_ERR_SHAPE;
     if (group_offsets != nullptr && (groups < 1 || groups > DSL_MAX_GROUPS)) return DSL_ERR_TOO_LARGE;
     if (ep->out_dtype != DSL_F32 && ep->out_dtype != DSL_BF16) return DSL_ERR_ENUM;
@@ -98,6 +101,7 @@ static int fill_common(GemmArgs& a, const void* A, const void* B, void* C, long 
     a.out_bf16 = ep->out_dtype == DSL_BF16;
     a.status = status;
     a.b_static = ep->b_is_static != 0;
+    a.act = ep->activation;
     if (ep->workspace != nullptr && aligned16(ep->workspace)) {
         a.partial = static_cast<float*>(ep->workspace);
         a.partial_bytes = ep->workspace_bytes;

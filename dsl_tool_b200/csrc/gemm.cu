@@ -427,7 +427,7 @@ static int forced_kernel() {
 }
 
 int choose_split_k(const GemmArgs& args, long long tiles) {
-    if (args.group_offsets != nullptr || args.partial == nullptr || tiles <= 0) return 1;
+    if (args.group_offsets != nullptr || args.partial == nullptr || tiles <= 0 || args.act != DSL_ACT_NONE) return 1;
     const int num_kb = (args.k_bytes + STAGE_KB - 1) / STAGE_KB;
     if (tiles * 2 > sm_count() || num_kb < 8) return 1;
     long long want = sm_count() / tiles;

@@ -37,6 +37,7 @@ struct GemmArgs {
     float* partial;              // [split_k, m_total, n] scratch (dense problems only)
     size_t partial_bytes;        // capacity of `partial`
     int b_static;                // B was complete before the preceding kernel of the stream was launched
+    int act;                     // DSL_ACT_*: SWIGLU turns column pairs (gate, up) into one output column
     uint32_t* status;
 };
 

@@ -20,6 +20,7 @@
 #include <string.h>
 
 #include "gemm.cuh"
+#include "gemm_epilogue.cuh"
 #include "gemm_tiles.cuh"
 #include "ptx.cuh"
 
@@ -199,43 +200,10 @@ gemm_fp8_groupwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             for (int c = 0; c < 4; ++c) {
                 const int col0 = col_base + c * 32;
                 if (col0 >= args.n) continue;
-                float f[32];
+                uint32_t v[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float x = __fmul_rn(__fmul_rn(acc[c * 32 + i], s1), s2);
-                    if (args.row_scale != nullptr) x = __fmul_rn(x, rs);
-                    if (args.col_scale != nullptr && col0 + i < args.n)
-                        x = __fmul_rn(x, args.col_scale[static_cast<size_t>(ti.group) * args.n + col0 + i]);
-                    f[i] = x;
-                }
-                const size_t off = static_cast<size_t>(row) * args.ldc + col0;
-                if (vec_ok && col0 + 32 <= args.n) {
-                    if (args.out_bf16) {
-                        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.c) + off);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                __nv_bfloat162 pr = __floats2bfloat162_rn(f[8 * i + 2 * j], f[8 * i + 2 * j + 1]);
-                                w[j] = *reinterpret_cast<uint32_t*>(&pr);
-                            }
-                            dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    } else {
-                        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.c) + off);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) dst[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (col0 + i < args.n) {
-                            if (args.out_bf16) static_cast<__nv_bfloat16*>(args.c)[off + i] = __float2bfloat16_rn(f[i]);
-                            else static_cast<float*>(args.c)[off + i] = f[i];
-                        }
-                    }
-                }
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(acc[c * 32 + i]);
+                store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
             }
         }
     }

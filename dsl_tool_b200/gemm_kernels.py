@@ -36,11 +36,29 @@ def _out_dtype(name) -> torch.dtype:
         raise ValueError(f"out_dtype must be float32 or bfloat16, got {name!r}") from None
 
 
+def _activation_code(activation: Optional[str]) -> int:
+    if activation is None or activation == "none":
+        return _lib.ACT_NONE
+    if activation == "swiglu":
+        return _lib.ACT_SWIGLU
+    raise ValueError(f"activation must be None or 'swiglu', got {activation!r}")
+
+
+def _out_cols(n: int, activation: Optional[str]) -> int:
+    """Columns of the result: n, or n/2 when (gate, up) column pairs are folded by the epilogue."""
+    if _activation_code(activation) == _lib.ACT_SWIGLU:
+        if n % 2:
+            raise ValueError("activation 'swiglu' needs an even number of GEMM columns")
+        return n // 2
+    return n
+
+
 def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
               row_scale: Optional[torch.Tensor], col_scale: Optional[torch.Tensor], keep: list,
-              b_static: bool = False) -> _lib.Epilogue:
+              b_static: bool = False, activation: Optional[str] = None) -> _lib.Epilogue:
     ep = _lib.Epilogue()
     ep.b_is_static = 1 if b_static else 0
+    ep.activation = _activation_code(activation)
     for name, s in (("a", scale_a), ("b", scale_b)):
         host, devp = 1.0, None
         if isinstance(s, torch.Tensor):
@@ -88,7 +106,7 @@ def _offsets_arg(offsets: Optional[torch.Tensor], dev) -> Tuple[Optional[torch.T
 
 def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, scale_b: Scalar, *, n: int,
                        out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
-                       row_scale=None, col_scale=None, b_static: bool = False) -> torch.Tensor:
+                       row_scale=None, col_scale=None, b_static: bool = False, activation: Optional[str] = None) -> torch.Tensor:
     """C = (qa @ qb^T) * scale_a * scale_b on E4M3 bytes; qa [M, K], qb_nk [G*N, K].
     `b_static`: the weight was complete before the previous kernel on this stream was launched
     (lets the decode kernel stream it while the activation quantiser still runs)."""
@@ -98,11 +116,12 @@ def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, s
     offs, groups = _offsets_arg(expert_offsets, dev)
     if qb_nk.shape != (groups * n, K):
         raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major bytes, got {tuple(qb_nk.shape)}")
-    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    nc = _out_cols(n, activation)
+    out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, scale_a, scale_b, out.dtype, row_scale, col_scale, keep, b_static)
+    ep = _epilogue(dev, scale_a, scale_b, out.dtype, row_scale, col_scale, keep, b_static, activation)
     with torch.cuda.device(dev):
-        rc = _lib.lib().dsl_gemm_fp8(qa.data_ptr(), qb_nk.data_ptr(), out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+        rc = _lib.lib().dsl_gemm_fp8(qa.data_ptr(), qb_nk.data_ptr(), out.data_ptr(), nc, M, n, K, _lib.ptr(offs),
                                      groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "dsl_gemm_fp8")
     return out
@@ -111,7 +130,7 @@ def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, s
 def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor, *,
                                  n: int, sb_block: bool, out_dtype=torch.float32,
                                  expert_offsets: Optional[torch.Tensor] = None,
-                                 row_scale=None, col_scale=None) -> torch.Tensor:
+                                 row_scale=None, col_scale=None, activation: Optional[str] = None) -> torch.Tensor:
     """C = sum_g (qa_g @ qb_g^T) * sa[:, g] * sb[g]; sa [M, K/128]; sb [G, K/128, N] per-column
     (sb_block False, the layout of cuda/gemm/fp8_gemm.cu:75) or [G, ceil(N/128), K/128] blocks."""
     dev = _lib.require_cuda(qa, qb_nk, sa, sb)
@@ -129,12 +148,13 @@ def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torc
     want_sb = groups * ((n + 127) // 128) * (K // 128) if sb_block else groups * (K // 128) * n
     if sb.numel() != want_sb:
         raise ValueError(f"scale_b must have {want_sb} elements, got {tuple(sb.shape)}")
-    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    nc = _out_cols(n, activation)
+    out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, None, None, out.dtype, row_scale, col_scale, keep)
+    ep = _epilogue(dev, None, None, out.dtype, row_scale, col_scale, keep, False, activation)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_fp8_groupwise(qa.data_ptr(), qb_nk.data_ptr(), sa.data_ptr(), sb.data_ptr(),
-                                               1 if sb_block else 0, out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+                                               1 if sb_block else 0, out.data_ptr(), nc, M, n, K, _lib.ptr(offs),
                                                groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(),
                                                _lib.stream_ptr())
     _lib.check(rc, "dsl_gemm_fp8_groupwise")
@@ -144,7 +164,7 @@ def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torc
 def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, *,
                        format: str, n: int, global_scale_a: Scalar = None, global_scale_b: Scalar = None,
                        out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
-                       row_scale=None, col_scale=None, b_static: bool = False) -> torch.Tensor:
+                       row_scale=None, col_scale=None, b_static: bool = False, activation: Optional[str] = None) -> torch.Tensor:
     """Block-scaled FP4 GEMM on packed e2m1 operands pa [M, K/2], pb_nk [G*N, K/2] with tiled
     scale bytes; for NVFP4 the result is multiplied once by global_scale_a * global_scale_b.
     `b_static` as in gemm_fp8_quantized."""
@@ -163,12 +183,13 @@ def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor,
     need_a = (((M + 127) // 128) if offs is None else 0) * katoms * 512
     if sfa.numel() < need_a or sfb.numel() < groups * ((n + 127) // 128) * katoms * 512:
         raise ValueError("scale buffers are smaller than the tiled layout needs")
-    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    nc = _out_cols(n, activation)
+    out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, global_scale_a, global_scale_b, out.dtype, row_scale, col_scale, keep, b_static)
+    ep = _epilogue(dev, global_scale_a, global_scale_b, out.dtype, row_scale, col_scale, keep, b_static, activation)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_fp4(pa.data_ptr(), pb_nk.data_ptr(), _bytes2d(sfa).data_ptr(),
-                                     _bytes2d(sfb).data_ptr(), fmt, out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+                                     _bytes2d(sfb).data_ptr(), fmt, out.data_ptr(), nc, M, n, K, _lib.ptr(offs),
                                      groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "dsl_gemm_fp4")
     return out
@@ -176,7 +197,7 @@ def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor,
 
 def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torch.float32,
                   expert_offsets: Optional[torch.Tensor] = None, scale_a: Scalar = None,
-                  scale_b: Scalar = None) -> torch.Tensor:
+                  scale_b: Scalar = None, activation: Optional[str] = None) -> torch.Tensor:
     dev = _lib.require_cuda(a, b_nk)
     a = a.to(torch.bfloat16).contiguous()
     b_nk = b_nk.to(torch.bfloat16).contiguous()
@@ -184,11 +205,12 @@ def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torc
     offs, groups = _offsets_arg(expert_offsets, dev)
     if b_nk.shape != (groups * n, K):
         raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major, got {tuple(b_nk.shape)}")
-    out = torch.empty((M, n), dtype=_out_dtype(out_dtype), device=dev)
+    nc = _out_cols(n, activation)
+    out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, scale_a, scale_b, out.dtype, None, None, keep)
+    ep = _epilogue(dev, scale_a, scale_b, out.dtype, None, None, keep, False, activation)
     with torch.cuda.device(dev):
-        rc = _lib.lib().dsl_gemm_bf16(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), n, M, n, K, _lib.ptr(offs),
+        rc = _lib.lib().dsl_gemm_bf16(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), nc, M, n, K, _lib.ptr(offs),
                                       groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "dsl_gemm_bf16")
     return out
@@ -199,15 +221,21 @@ def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torc
 # --------------------------------------------------------------------------------------
 
 def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
-           expert_offsets: Optional[torch.Tensor] = None, row_scale=None, col_scale=None) -> torch.Tensor:
+           expert_offsets: Optional[torch.Tensor] = None, row_scale=None, col_scale=None,
+           activation: Optional[str] = None) -> torch.Tensor:
     """a [M, K] high-precision activations x packed weight -> [M, N]: quantise the activations
     in the weight's format (one pass on the GPU) and run the matching GEMM.  The packed weight is
-    treated as complete (the activation quantiser always sits between its producer and the GEMM)."""
+    treated as complete (the activation quantiser always sits between its producer and the GEMM).
+    activation "swiglu": the weight is a fused gate/up projection packed with `gate_up_interleave=True`;
+    the result is [M, N/2] = silu(gate) * up, computed in the GEMM epilogue
+    (cuda/activations/fused_gated_activations.cu:75-90 without the [M, N] round trip through memory)."""
+    if _activation_code(activation) == _lib.ACT_SWIGLU and not w.gate_up_interleaved:
+        raise ValueError("activation 'swiglu' needs a weight packed with gate_up_interleave=True")
     if a.dim() != 2 or a.shape[1] != w.k:
         raise ValueError(f"activations must be [M, {w.k}], got {tuple(a.shape)}")
     if w.groups > 1 and expert_offsets is None:
         raise ValueError("a multi-group weight needs expert_offsets")
-    common = dict(n=w.n, out_dtype=out_dtype, expert_offsets=expert_offsets)
+    common = dict(n=w.n, out_dtype=out_dtype, expert_offsets=expert_offsets, activation=activation)
     if w.format == "bf16":
         return gemm_bf16_raw(a, w.q, **common)
     if w.format == "fp8":
@@ -380,7 +408,8 @@ def _fp4_gemm_ref32(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, sca
 
 
 def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_offsets: Optional[torch.Tensor] = None,
-                 *, format: str = "bf16", b_layout: str = "kn", out_dtype=None, cache_weights: bool = False) -> torch.Tensor:
+                 *, format: str = "bf16", b_layout: str = "kn", out_dtype=None, cache_weights: bool = False,
+                 activation: Optional[str] = None) -> torch.Tensor:
     """Grouped GEMM for MoE / LoRA (triton/gemm/gemm_kernels.py:164-182, tilelang/gemm/gemm_kernels.py:116-133).
 
     Fixed-size groups: A [G,M,K], B [G,K,N] -> [G,M,N] (the reference's form; `num_groups`
@@ -390,8 +419,11 @@ def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_of
     format "bf16" multiplies unquantised (result in A.dtype, as the Triton reference); "fp8",
     "fp8_groupwise", "nvfp4", "mxfp4" quantise A and B on the GPU first (result fp32 unless
     out_dtype says otherwise).  B may be a PackedWeight.  b_layout "kn": B [G,K,N]; "nk": [G,N,K].
-    `cache_weights` as in fp8_gemm.
+    `cache_weights` as in fp8_gemm.  activation "swiglu": B is a fused gate/up projection (N = 2H, gate rows
+    first, the input layout of the reference's swiglu); the result has H columns, silu(gate) * up, computed
+    in the GEMM epilogue.  A PackedWeight passed as B must have been packed with `gate_up_interleave=True`.
     """
+    glu = _activation_code(activation) == _lib.ACT_SWIGLU
     formats = {"bf16": "bf16", "fp8": "fp8", "fp8_groupwise": "fp8_block128", "nvfp4": "nvfp4", "mxfp4": "mxfp4"}
     if format not in formats:
         raise ValueError(f"format must be one of {sorted(formats)}, got {format!r}")
@@ -406,7 +438,8 @@ def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_of
     else:
         if B.dim() != 3:
             raise ValueError(f"B must be 3-D, got {tuple(B.shape)}")
-        w = cached_pack(B, formats[format], b_layout) if cache_weights else pack_weight(B, formats[format], layout=b_layout)
+        w = (cached_pack(B, formats[format], b_layout, gate_up_interleave=glu) if cache_weights
+             else pack_weight(B, formats[format], layout=b_layout, gate_up_interleave=glu))
     G = w.groups
     if num_groups is not None and int(num_groups) != G:
         raise ValueError(f"num_groups={num_groups} but B holds {G} groups")
@@ -425,8 +458,8 @@ def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_of
         out_dtype = A.dtype if (format == "bf16" and A.dtype in (torch.float32, torch.bfloat16)) else torch.float32
     if G == 1:
         offs = None
-    out = linear(a2.contiguous(), w, out_dtype=out_dtype, expert_offsets=offs)
-    return out.reshape(G, Mg, w.n) if fixed else out
+    out = linear(a2.contiguous(), w, out_dtype=out_dtype, expert_offsets=offs, activation=activation)
+    return out.reshape(G, Mg, out.shape[1]) if fixed else out
 
 
 def bf16_gemm(A: torch.Tensor, B: torch.Tensor, *, b_layout: str = "kn", out_dtype="float32") -> torch.Tensor:

@@ -149,17 +149,21 @@ class PackedWeight:
     groups: int
     n: int
     k: int
+    gate_up_interleaved: bool = False   # rows reordered to (gate_0, up_0, gate_1, up_1, ...) for the fused SwiGLU epilogue
 
 
-def pack_weight(w: torch.Tensor, format: str, layout: str = "nk",
-                global_scale: Union[None, float, torch.Tensor] = None) -> PackedWeight:
+def _pack_weight_impl(w: torch.Tensor, format: str, layout: str = "nk",
+                global_scale: Union[None, float, torch.Tensor] = None, gate_up_interleave: bool = False) -> PackedWeight:
     """Quantise a weight for the GEMM entry points.
 
     w is [N, K] / [G, N, K] (layout "nk") or the reference's [K, N] / [G, K, N] (layout "kn",
     cuda/gemm/fp8_gemm.cu:29-35); it is made K-major first.  `global_scale` (NVFP4 only) fixes the
     fp32 global scale instead of deriving it from this tensor's amax - pass the unsharded tensor's
     amax/2688 when packing a column or expert shard so that every shard quantises exactly as the
-    whole weight would.
+    whole weight would.  `gate_up_interleave`: the N = 2H output rows are a fused gate/up projection
+    ([gate; up], the input layout of the reference's swiglu, cuda/activations/fused_gated_activations.cu:75-90);
+    they are reordered to gate_0, up_0, gate_1, up_1, ... so that `linear(..., activation="swiglu")` can fold
+    each pair in the GEMM epilogue.
     """
     dev = _lib.require_cuda(w)
     if layout not in ("nk", "kn"):
@@ -170,6 +174,11 @@ def pack_weight(w: torch.Tensor, format: str, layout: str = "nk",
         raise ValueError("weight must be 2-D or 3-D")
     if layout == "kn":
         w = w.transpose(1, 2)
+    if gate_up_interleave:
+        if w.shape[1] % 2:
+            raise ValueError("gate_up_interleave needs an even number of output rows")
+        h = w.shape[1] // 2
+        w = torch.stack((w[:, :h], w[:, h:]), dim=2).reshape(w.shape[0], 2 * h, w.shape[2])
     w = w.contiguous()
     G, N, K = w.shape
     flat = w.reshape(G * N, K)
@@ -203,3 +212,13 @@ def pack_weight(w: torch.Tensor, format: str, layout: str = "nk",
             q, sf, gs = quantize_fp4(flat, format, global_scale=gs_val, group_offsets=offs)
         return PackedWeight(format, q, sf, gs, G, N, K)
     raise ValueError(f"unknown weight format {format!r}")
+
+
+def pack_weight(w: torch.Tensor, format: str, layout: str = "nk",
+                global_scale: Union[None, float, torch.Tensor] = None, gate_up_interleave: bool = False) -> PackedWeight:
+    packed = _pack_weight_impl(w, format, layout, global_scale, gate_up_interleave)
+    packed.gate_up_interleaved = bool(gate_up_interleave)
+    return packed
+
+
+pack_weight.__doc__ = _pack_weight_impl.__doc__

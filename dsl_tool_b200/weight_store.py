@@ -50,7 +50,8 @@ def save_packed(path: Union[str, os.PathLike], w: PackedWeight) -> None:
     if w.format not in _FORMATS:
         raise ValueError(f"unknown packed-weight format {w.format!r}")
     header: Dict[str, object] = {"__metadata__": {"producer": "dsl_tool_b200", "format": w.format, "groups": str(w.groups),
-                                                  "n": str(w.n), "k": str(w.k)}}
+                                                  "n": str(w.n), "k": str(w.k),
+                                                  "gate_up_interleaved": "1" if w.gate_up_interleaved else "0"}}
     blobs = []
     pos = 0
     for name, t in (("q", w.q), ("scale", w.scale), ("global_scale", w.global_scale)):
@@ -113,7 +114,7 @@ def load_packed(path: Union[str, os.PathLike], device: Union[str, torch.device] 
     if tensors["q"] is None:
         raise ValueError(f"{path}: no tensor 'q'")
     return PackedWeight(meta["format"], tensors["q"], tensors["scale"], tensors["global_scale"], int(meta["groups"]),
-                        int(meta["n"]), int(meta["k"]))
+                        int(meta["n"]), int(meta["k"]), meta.get("gate_up_interleaved", "0") == "1")
 
 
 # ---- identity cache -----------------------------------------------------------------------
@@ -144,15 +145,15 @@ class WeightCache:
         self.hits = 0
         self.misses = 0
 
-    def get(self, w: torch.Tensor, format: str, layout: str = "nk", packer=pack_weight) -> PackedWeight:
-        key = _identity(w) + (format, layout)
+    def get(self, w: torch.Tensor, format: str, layout: str = "nk", packer=pack_weight, **pack_kwargs) -> PackedWeight:
+        key = _identity(w) + (format, layout) + tuple(sorted(pack_kwargs.items()))
         with self._lock:
             hit = self._items.get(key)
             if hit is not None:
                 self._items.move_to_end(key)
                 self.hits += 1
                 return hit[1]
-        packed = packer(w, format, layout)
+        packed = packer(w, format, layout, **pack_kwargs)
         size = packed_nbytes(packed)
         with self._lock:
             self.misses += 1
@@ -182,9 +183,9 @@ _file_cache: Dict[Tuple[str, str], Tuple[float, int, PackedWeight]] = {}
 _file_lock = threading.Lock()
 
 
-def cached_pack(w: torch.Tensor, format: str, layout: str = "nk") -> PackedWeight:
+def cached_pack(w: torch.Tensor, format: str, layout: str = "nk", **pack_kwargs) -> PackedWeight:
     """`pack_weight` through the process-wide identity cache."""
-    return _default_cache.get(w, format, layout)
+    return _default_cache.get(w, format, layout, **pack_kwargs)
 
 
 def default_cache() -> WeightCache:

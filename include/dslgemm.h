@@ -83,6 +83,8 @@ int dsl_quant_fp4(const void* x, int dtype, long long rows, long long cols, int 
  * (cuda/gemm/fp8_gemm.cu:29-35, B[k*N+n]) into the K-major [N, K] the tensor cores read. */
 int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream);
 
+enum { DSL_ACT_NONE = 0, DSL_ACT_SWIGLU = 1 };
+
 /* Epilogue description shared by the GEMM entry points.
  *   out = acc * scale_a * scale_b [* row_scale[m]] [* col_scale[g*N+n]]
  * scale_x is *scale_x_dev when that pointer is non-NULL, else scale_x_host.
@@ -103,6 +105,12 @@ typedef struct {
                                    kernel is launched with programmatic stream serialisation and then starts
                                    fetching B while that predecessor (e.g. the activation quantiser) still runs;
                                    A, its scales and every output are touched only after the predecessor is done. */
+    int activation;             /* DSL_ACT_NONE, or DSL_ACT_SWIGLU: the GEMM's columns are (gate, up) pairs - column 2j
+                                   is gate_j, column 2j+1 is up_j, i.e. the weight rows were interleaved when it was
+                                   packed - and C is [M_total, N/2] with C[m,j] = silu(gate) * up computed in fp32 on
+                                   the fully scaled values, silu(x) = x / (1 + exp(-x)); ldc >= N/2.  Fuses the
+                                   reference's swiglu (cuda/activations/fused_gated_activations.cu:27-29,75-90) into
+                                   the epilogue of the gate/up projection. */
 } dsl_epilogue;
 
 /*
