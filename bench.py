@@ -47,6 +47,8 @@ WORKLOADS = {
     "moe_nvfp4": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
     "moe_fp8_groupwise": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
     "moe_nvfp4_swiglu": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02, act="swiglu"),
+    "moe_nvfp4_swiglu_nvfp4out": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
+                                      act="swiglu", out="nvfp4"),
     "moe_fp8_groupwise_swiglu": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
                                      act="swiglu"),
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
@@ -153,11 +155,14 @@ def build_workload(name, rank, world, device, sets, strong=False):
     torch.cuda.synchronize()
 
     def step(i, a=None):
+        if cfg.get("out") == "nvfp4":    # result quantised in the epilogue with a fixed (calibrated) global scale
+            return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype="nvfp4", out_global_scale=1.0 / 2688.0,
+                          expert_offsets=offs, activation=cfg.get("act"))[0]
         return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype=torch.bfloat16, expert_offsets=offs,
                       activation=cfg.get("act"))
 
     return dict(step=step, acts=acts, wts=wts, offs=offs, M=M, K=K, N=N, kind=kind, flops=2.0 * M * N * K,
-                moe=bool(cfg.get("moe")), act=cfg.get("act"))
+                moe=bool(cfg.get("moe")), act=cfg.get("act"), out=cfg.get("out"))
 
 
 def split_step(wl):
@@ -179,6 +184,8 @@ def split_step(wl):
     def gemm(i, q):
         w = wl["wts"][i % sets]
         common = dict(n=w.n, out_dtype=torch.bfloat16, expert_offsets=offs, activation=wl.get("act"))
+        if wl.get("out") == "nvfp4":
+            common.update(out_dtype="nvfp4", out_global_scale=1.0 / 2688.0)
         if kind == "fp8":
             return GK.gemm_fp8_quantized(q[0], w.q, q[1], w.scale, b_static=True, **common)
         if kind == "fp8_block128":
@@ -350,7 +357,10 @@ def main():
         h.copy_(wl["acts"][j % len(wl["acts"])])
     dev_a = torch.empty_like(wl["acts"][0])
     out_cols = wl["N"] // 2 if wl.get("act") else wl["N"]
-    host_out = torch.empty((wl["M"], out_cols), dtype=torch.bfloat16).pin_memory()
+    if wl.get("out") == "nvfp4":
+        host_out = torch.empty((wl["M"], out_cols // 2), dtype=torch.uint8).pin_memory()
+    else:
+        host_out = torch.empty((wl["M"], out_cols), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(K_steps, 10))
     for i in range(2):
         dev_a.copy_(host_a[i % 2], non_blocking=True)
@@ -403,7 +413,8 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": DTYPE_NAME[kind], "data": "synthetic",
         "config": {"workload": args.workload, "M": wl["M"], "K": wl["K"], "N": wl["N"],
-                   "out": "bf16" if not wl.get("act") else "bf16 [M, N/2] = silu(gate) * up, folded in the GEMM epilogue",
+                   "out": ("bf16" if not wl.get("act") else "bf16 [M, N/2] = silu(gate) * up, folded in the GEMM epilogue")
+                   if not wl.get("out") else "NVFP4 [M, N/2] = quantise(silu(gate) * up), both folded in the GEMM epilogue",
                    "moe": wl["moe"], "per_rank": ("own weight shard / experts of this size, no collective" if args.scaling == "weak" else
                                 "this rank's column range / experts of the one problem, no collective"),
                    "step": "activation quantise + GEMM, weights quantised once",
@@ -413,7 +424,7 @@ def main():
                      "kernel": "gemm", "kernel_ms": gemm_ms, "quant_kernel_ms": quant_ms,
                      "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"},
         "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": wl["M"] * out_cols * 2,
+                "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * host_out.element_size(),
                 "ms_per_step": e2e_ms},
         # kernels of this library per step: quantiser passes + one GEMM kernel (NVFP4 tensors of up to
         # 2^18 elements are quantised by a single launch, larger ones by an amax pass + a quantise pass)

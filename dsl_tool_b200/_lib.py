@@ -20,6 +20,7 @@ F32, BF16, F16 = 0, 1, 2
 FP8_PER_TENSOR, FP8_GROUP_1X128, FP8_BLOCK_128X128 = 0, 1, 2
 FP4_NV, FP4_MX = 0, 1
 ACT_NONE, ACT_SWIGLU = 0, 1
+OUT_NVFP4 = 3
 MAX_GROUPS = 1024
 STATIC_SCRATCH_BYTES = 4 << 20
 
@@ -48,6 +49,9 @@ class Epilogue(ctypes.Structure):
         ("workspace_bytes", ctypes.c_size_t),
         ("b_is_static", ctypes.c_int),
         ("activation", ctypes.c_int),
+        ("out_sf", ctypes.c_void_p),
+        ("out_gs_host", ctypes.c_float),
+        ("out_gs_dev", ctypes.c_void_p),
     ]
 
 

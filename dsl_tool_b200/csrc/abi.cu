@@ -82,7 +82,14 @@ static int fill_common(GemmArgs& a, const void* A, const void* B, void* C, long 
     if (M_total < 0 || N < 0 || k_bytes <= 0 || M_total > 0x7FFFFFFFll || ldc < (glu ? N / 2 : N)) return DSL_ERR_SHAPE;
     if (k_bytes % 16 != 0) return DSL_ERR_SHAPE;
     if (group_offsets != nullptr && (groups < 1 || groups > DSL_MAX_GROUPS)) return DSL_ERR_TOO_LARGE;
-    if (ep->out_dtype != DSL_F32 && ep->out_dtype != DSL_BF16) return DSL_ERR_ENUM;
+    if (ep->out_dtype != DSL_F32 && ep->out_dtype != DSL_BF16 && ep->out_dtype != DSL_OUT_NVFP4) return DSL_ERR_ENUM;
+    const int n_out = glu ? N / 2 : N;
+    if (ep->out_dtype == DSL_OUT_NVFP4) {
+        if (ep->out_sf == nullptr) return DSL_ERR_NULL;
+        if (n_out % 16 != 0 || ldc % 16 != 0) return DSL_ERR_SHAPE;
+        if (!aligned16(ep->out_sf)) return DSL_ERR_ALIGN;
+        if (ep->out_gs_dev == nullptr && !(ep->out_gs_host > 0.f)) return DSL_ERR_SHAPE;
+    }
     if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return DSL_ERR_ALIGN;
     a = GemmArgs{};
     a.m_total = static_cast<int>(M_total);
@@ -102,6 +109,12 @@ static int fill_common(GemmArgs& a, const void* A, const void* B, void* C, long 
     a.status = status;
     a.b_static = ep->b_is_static != 0;
     a.act = ep->activation;
+    if (ep->out_dtype == DSL_OUT_NVFP4) {
+        a.out_sf = static_cast<uint8_t*>(ep->out_sf);
+        a.out_gs = ep->out_gs_host;
+        a.out_gs_dev = ep->out_gs_dev;
+        a.out_sf_katoms = (n_out / 16 + 3) / 4;
+    }
     if (ep->workspace != nullptr && aligned16(ep->workspace)) {
         a.partial = static_cast<float*>(ep->workspace);
         a.partial_bytes = ep->workspace_bytes;
@@ -136,6 +149,7 @@ int dsl_gemm_fp8_groupwise(const uint8_t* A, const uint8_t* B, const float* sa, 
     if (K % 128 != 0) return DSL_ERR_SHAPE;
     int rc = fill_common(a, A, B, C, ldc, M_total, N, K, group_offsets, groups, ep, status);
     if (rc != 0) return rc;
+    if (a.out_sf != nullptr) return DSL_ERR_ENUM;    // quantised output: not in the group-scaled kernels
     a.gsa = sa;
     a.gsb = sb;
     a.sb_block = sb_block != 0;

@@ -271,7 +271,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                             if (col0 + i < args.n) dst[i] = __uint_as_float(v[i]);
                     }
                 } else {
-                    store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
+                    store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok, ti.mtile, quad * 32 + lane);
                 }
             }
             tc_fence_before();
@@ -427,7 +427,7 @@ static int forced_kernel() {
 }
 
 int choose_split_k(const GemmArgs& args, long long tiles) {
-    if (args.group_offsets != nullptr || args.partial == nullptr || tiles <= 0 || args.act != DSL_ACT_NONE) return 1;
+    if (args.group_offsets != nullptr || args.partial == nullptr || tiles <= 0 || args.act != DSL_ACT_NONE || args.out_sf != nullptr) return 1;
     const int num_kb = (args.k_bytes + STAGE_KB - 1) / STAGE_KB;
     if (tiles * 2 > sm_count() || num_kb < 8) return 1;
     long long want = sm_count() / tiles;

@@ -38,6 +38,10 @@ struct GemmArgs {
     size_t partial_bytes;        // capacity of `partial`
     int b_static;                // B was complete before the preceding kernel of the stream was launched
     int act;                     // DSL_ACT_*: SWIGLU turns column pairs (gate, up) into one output column
+    uint8_t* out_sf;             // non-null: the result is quantised to NVFP4 (c = packed bytes, out_sf = scale tiles)
+    float out_gs;                // its global scale (host value) ...
+    const float* out_gs_dev;     // ... overridden by this device scalar when non-null
+    int out_sf_katoms;           // 512-byte scale tiles along the output row = ceil(ceil(Nout/16)/4)
     uint32_t* status;
 };
 

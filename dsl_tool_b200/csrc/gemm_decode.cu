@@ -577,7 +577,9 @@ static int launch_decode_kind(const void* A, const void* B, const GemmArgs& args
 
 // Returns DSL_NOT_SERVED when the problem is not one this kernel serves (the caller then uses the tiled kernels).
 int launch_gemm_decode(int kind, const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
-    if (args.group_offsets != nullptr || args.m_total > DSL_DECODE_MAX_ROWS || args.act != DSL_ACT_NONE) return DSL_NOT_SERVED;
+    if (args.group_offsets != nullptr || args.m_total > DSL_DECODE_MAX_ROWS || args.act != DSL_ACT_NONE ||
+        args.out_sf != nullptr)
+        return DSL_NOT_SERVED;
     switch (kind) {
         case KIND_F8: return launch_decode_kind<KIND_F8>(A, B, args, st);
         case KIND_NVF4: return launch_decode_kind<KIND_NVF4>(A, B, args, st);

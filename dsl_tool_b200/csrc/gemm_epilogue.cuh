@@ -5,14 +5,46 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include <float.h>
+
 #include "gemm.cuh"
+#include "ptx.cuh"
 
 namespace dsl {
 
+// One NVFP4 block of the result: 16 consecutive output columns of one row -> 8 packed bytes + one
+// scale byte in the tile layout, with the arithmetic of the NVFP4 quantiser (quant.cu):
+//   sf = ue4m3_rne(min((amax/6)/gs, 448)),  q = e2m1_rne(x * (1 / (f32(sf) * gs))).
+// `sf_tile` is the 128-row scale tile the row belongs to, `rin` the row's index inside it.
+__device__ __forceinline__ void store_nvfp4_block(const GemmArgs& args, int row, int ocol0, const float* x, float gs,
+                                                  int sf_tile, int rin) {
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(x[i]));
+    float t = __fdiv_rn(__fdiv_rn(m, 6.0f), gs);
+    t = fminf(t, 448.0f);
+    const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
+    const float d = __fmul_rn(e4m3_to_float(sfb), gs);
+    const float inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t b = cvt_e2m1x2(__fmul_rn(x[2 * i], inv), __fmul_rn(x[2 * i + 1], inv));
+        w[i >> 2] |= b << (8 * (i & 3));
+    }
+    uint8_t* c = static_cast<uint8_t*>(args.c);
+    *reinterpret_cast<uint2*>(c + static_cast<size_t>(row) * (args.ldc >> 1) + (ocol0 >> 1)) = make_uint2(w[0], w[1]);
+    const int blk = ocol0 >> 4;
+    args.out_sf[(static_cast<size_t>(sf_tile) * args.out_sf_katoms + (blk >> 2)) * 512 + (rin & 31) * 16 + (rin >> 5) * 4 + (blk & 3)] =
+        static_cast<uint8_t>(sfb);
+}
+
 // v: 32 fp32 accumulators (bit patterns) of row `row`, columns col0..col0+31 of group `group`.
 // out = (acc * s1) * s2 [* row_scale[row]] [* col_scale[group*n + col]]
+// sf_tile / rin: only read when the result is quantised (args.out_sf != nullptr).
 __device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int col0, int group,
-                                              const uint32_t (&v)[32], float s1, float s2, float rs, bool vec_ok) {
+                                              const uint32_t (&v)[32], float s1, float s2, float rs, bool vec_ok,
+                                              int sf_tile = 0, int rin = 0) {
     float f[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -37,6 +69,10 @@ __device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int
             o[j] = __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), f[2 * j + 1]);
         }
         const int c0 = col0 >> 1;
+        if (args.out_sf != nullptr) {     // n/2 is a multiple of 16 here, so the 16 outputs are one whole block
+            if (col0 < args.n) store_nvfp4_block(args, row, c0, o, args.out_gs_dev != nullptr ? *args.out_gs_dev : args.out_gs, sf_tile, rin);
+            return;
+        }
         const size_t off = static_cast<size_t>(row) * args.ldc + c0;
         if (vec_ok && col0 + 32 <= args.n) {
             if (args.out_bf16) {
@@ -65,6 +101,12 @@ __device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int
                 }
             }
         }
+        return;
+    }
+    if (args.out_sf != nullptr) {         // n is a multiple of 16: one or two whole blocks in this chunk
+        const float gs = args.out_gs_dev != nullptr ? *args.out_gs_dev : args.out_gs;
+        if (col0 < args.n) store_nvfp4_block(args, row, col0, f, gs, sf_tile, rin);
+        if (col0 + 16 < args.n) store_nvfp4_block(args, row, col0 + 16, f + 16, gs, sf_tile, rin);
         return;
     }
     const size_t off = static_cast<size_t>(row) * args.ldc + col0;

@@ -330,7 +330,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (lane == 0) mbar_arrive_cluster(ovl_free, 0);
                 }
                 const int col0 = ti.n0 + c * 32;
-                if (row_ok && col0 < args.n) store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
+                if (row_ok && col0 < args.n)
+                    store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok, ti.sf_tile + static_cast<int>(rank), quad * 32 + lane);
             }
             tc_fence_before();
             __syncwarp();

@@ -53,6 +53,40 @@ def _out_cols(n: int, activation: Optional[str]) -> int:
     return n
 
 
+def _is_nvfp4_out(out_dtype) -> bool:
+    return isinstance(out_dtype, str) and out_dtype.lower() == "nvfp4"
+
+
+def _make_output(dev, M: int, nc: int, out_dtype, out_global_scale: Scalar, offs, groups: int, ep: "_lib.Epilogue", keep: list):
+    """Allocates the result and completes the epilogue description.  Returns (tensor handed to the kernel,
+    leading dimension in elements, value to return to the caller).  out_dtype "nvfp4": the result is quantised
+    in the GEMM epilogue with `out_global_scale`; the caller gets (packed bytes [M, nc/2], scale tiles, global
+    scale [1]) - exactly what quantize_fp4(result, "nvfp4", global_scale=...) would give - ready to be the A
+    operand of the next FP4 GEMM."""
+    if not _is_nvfp4_out(out_dtype):
+        out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
+        ep.out_dtype = _lib.F32 if out.dtype == torch.float32 else _lib.BF16
+        return out, nc, out
+    if out_global_scale is None:
+        raise ValueError("out_dtype 'nvfp4' needs out_global_scale (the fp32 global scale of the quantised result)")
+    if nc % 16:
+        raise ValueError(f"out_dtype 'nvfp4' needs a multiple of 16 output columns, got {nc}")
+    out = torch.empty((M, nc // 2), dtype=torch.uint8, device=dev)
+    nblk = nc // 16
+    nbytes = _lib.lib().dsl_sf_bytes(M, nblk) if offs is None else _lib.lib().dsl_sf_bytes_grouped(M, nblk, groups)
+    sf = torch.zeros(int(nbytes), dtype=torch.uint8, device=dev)
+    if isinstance(out_global_scale, torch.Tensor):
+        gs = out_global_scale.detach().to(device=dev, dtype=torch.float32).reshape(1)
+    else:
+        gs = torch.full((1,), float(out_global_scale), dtype=torch.float32, device=dev)
+    keep.extend((sf, gs))
+    ep.out_dtype = _lib.OUT_NVFP4
+    ep.out_sf = sf.data_ptr()
+    ep.out_gs_host = 1.0
+    ep.out_gs_dev = gs.data_ptr()
+    return out, nc, (out, sf, gs)
+
+
 def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
               row_scale: Optional[torch.Tensor], col_scale: Optional[torch.Tensor], keep: list,
               b_static: bool = False, activation: Optional[str] = None) -> _lib.Epilogue:
@@ -76,7 +110,7 @@ def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
             t = t.detach().to(device=dev, dtype=torch.float32).contiguous()
             keep.append(t)
             setattr(ep, name, t.data_ptr())
-    ep.out_dtype = _lib.F32 if out == torch.float32 else _lib.BF16
+    ep.out_dtype = _lib.F32 if out in (None, torch.float32) else _lib.BF16
     ws = _lib.workspace(dev)
     ep.workspace = ws.data_ptr()
     ep.workspace_bytes = ws.numel()
@@ -106,7 +140,8 @@ def _offsets_arg(offsets: Optional[torch.Tensor], dev) -> Tuple[Optional[torch.T
 
 def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, scale_b: Scalar, *, n: int,
                        out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
-                       row_scale=None, col_scale=None, b_static: bool = False, activation: Optional[str] = None) -> torch.Tensor:
+                       row_scale=None, col_scale=None, b_static: bool = False, activation: Optional[str] = None,
+                       out_global_scale: Scalar = None):
     """C = (qa @ qb^T) * scale_a * scale_b on E4M3 bytes; qa [M, K], qb_nk [G*N, K].
     `b_static`: the weight was complete before the previous kernel on this stream was launched
     (lets the decode kernel stream it while the activation quantiser still runs)."""
@@ -117,14 +152,14 @@ def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, s
     if qb_nk.shape != (groups * n, K):
         raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major bytes, got {tuple(qb_nk.shape)}")
     nc = _out_cols(n, activation)
-    out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, scale_a, scale_b, out.dtype, row_scale, col_scale, keep, b_static, activation)
+    ep = _epilogue(dev, scale_a, scale_b, None, row_scale, col_scale, keep, b_static, activation)
+    out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
     with torch.cuda.device(dev):
-        rc = _lib.lib().dsl_gemm_fp8(qa.data_ptr(), qb_nk.data_ptr(), out.data_ptr(), nc, M, n, K, _lib.ptr(offs),
+        rc = _lib.lib().dsl_gemm_fp8(qa.data_ptr(), qb_nk.data_ptr(), out.data_ptr(), ldc, M, n, K, _lib.ptr(offs),
                                      groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "dsl_gemm_fp8")
-    return out
+    return ret
 
 
 def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torch.Tensor, sb: torch.Tensor, *,
@@ -148,6 +183,8 @@ def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torc
     want_sb = groups * ((n + 127) // 128) * (K // 128) if sb_block else groups * (K // 128) * n
     if sb.numel() != want_sb:
         raise ValueError(f"scale_b must have {want_sb} elements, got {tuple(sb.shape)}")
+    if _is_nvfp4_out(out_dtype):
+        raise ValueError("a quantised result is not available from the group-scaled FP8 GEMM")
     nc = _out_cols(n, activation)
     out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
@@ -164,7 +201,8 @@ def gemm_fp8_groupwise_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, sa: torc
 def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor, *,
                        format: str, n: int, global_scale_a: Scalar = None, global_scale_b: Scalar = None,
                        out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
-                       row_scale=None, col_scale=None, b_static: bool = False, activation: Optional[str] = None) -> torch.Tensor:
+                       row_scale=None, col_scale=None, b_static: bool = False, activation: Optional[str] = None,
+                       out_global_scale: Scalar = None):
     """Block-scaled FP4 GEMM on packed e2m1 operands pa [M, K/2], pb_nk [G*N, K/2] with tiled
     scale bytes; for NVFP4 the result is multiplied once by global_scale_a * global_scale_b.
     `b_static` as in gemm_fp8_quantized."""
@@ -184,20 +222,20 @@ def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor,
     if sfa.numel() < need_a or sfb.numel() < groups * ((n + 127) // 128) * katoms * 512:
         raise ValueError("scale buffers are smaller than the tiled layout needs")
     nc = _out_cols(n, activation)
-    out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, global_scale_a, global_scale_b, out.dtype, row_scale, col_scale, keep, b_static, activation)
+    ep = _epilogue(dev, global_scale_a, global_scale_b, None, row_scale, col_scale, keep, b_static, activation)
+    out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_fp4(pa.data_ptr(), pb_nk.data_ptr(), _bytes2d(sfa).data_ptr(),
-                                     _bytes2d(sfb).data_ptr(), fmt, out.data_ptr(), nc, M, n, K, _lib.ptr(offs),
+                                     _bytes2d(sfb).data_ptr(), fmt, out.data_ptr(), ldc, M, n, K, _lib.ptr(offs),
                                      groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "dsl_gemm_fp4")
-    return out
+    return ret
 
 
 def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torch.float32,
                   expert_offsets: Optional[torch.Tensor] = None, scale_a: Scalar = None,
-                  scale_b: Scalar = None, activation: Optional[str] = None) -> torch.Tensor:
+                  scale_b: Scalar = None, activation: Optional[str] = None, out_global_scale: Scalar = None):
     dev = _lib.require_cuda(a, b_nk)
     a = a.to(torch.bfloat16).contiguous()
     b_nk = b_nk.to(torch.bfloat16).contiguous()
@@ -206,14 +244,14 @@ def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torc
     if b_nk.shape != (groups * n, K):
         raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major, got {tuple(b_nk.shape)}")
     nc = _out_cols(n, activation)
-    out = torch.empty((M, nc), dtype=_out_dtype(out_dtype), device=dev)
     keep: list = []
-    ep = _epilogue(dev, scale_a, scale_b, out.dtype, None, None, keep, False, activation)
+    ep = _epilogue(dev, scale_a, scale_b, None, None, None, keep, False, activation)
+    out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
     with torch.cuda.device(dev):
-        rc = _lib.lib().dsl_gemm_bf16(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), nc, M, n, K, _lib.ptr(offs),
+        rc = _lib.lib().dsl_gemm_bf16(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), ldc, M, n, K, _lib.ptr(offs),
                                       groups, ctypes.byref(ep), _lib.status_word(dev).data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "dsl_gemm_bf16")
-    return out
+    return ret
 
 
 # --------------------------------------------------------------------------------------
@@ -222,13 +260,15 @@ def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torc
 
 def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
            expert_offsets: Optional[torch.Tensor] = None, row_scale=None, col_scale=None,
-           activation: Optional[str] = None) -> torch.Tensor:
+           activation: Optional[str] = None, out_global_scale: Scalar = None):
     """a [M, K] high-precision activations x packed weight -> [M, N]: quantise the activations
     in the weight's format (one pass on the GPU) and run the matching GEMM.  The packed weight is
     treated as complete (the activation quantiser always sits between its producer and the GEMM).
     activation "swiglu": the weight is a fused gate/up projection packed with `gate_up_interleave=True`;
     the result is [M, N/2] = silu(gate) * up, computed in the GEMM epilogue
-    (cuda/activations/fused_gated_activations.cu:75-90 without the [M, N] round trip through memory)."""
+    (cuda/activations/fused_gated_activations.cu:75-90 without the [M, N] round trip through memory).
+    out_dtype "nvfp4" (with `out_global_scale`): the result is quantised in the same epilogue and returned as
+    (packed bytes, scale tiles, global scale), the A operand of a following `gemm_fp4_quantized`."""
     if _activation_code(activation) == _lib.ACT_SWIGLU and not w.gate_up_interleaved:
         raise ValueError("activation 'swiglu' needs a weight packed with gate_up_interleave=True")
     if a.dim() != 2 or a.shape[1] != w.k:
@@ -236,6 +276,10 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
     if w.groups > 1 and expert_offsets is None:
         raise ValueError("a multi-group weight needs expert_offsets")
     common = dict(n=w.n, out_dtype=out_dtype, expert_offsets=expert_offsets, activation=activation)
+    if _is_nvfp4_out(out_dtype):
+        if w.format == "fp8_block128":
+            raise ValueError("a quantised result is not available from the group-scaled FP8 GEMM")
+        common["out_global_scale"] = out_global_scale
     if w.format == "bf16":
         return gemm_bf16_raw(a, w.q, **common)
     if w.format == "fp8":

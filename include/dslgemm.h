@@ -84,6 +84,7 @@ int dsl_quant_fp4(const void* x, int dtype, long long rows, long long cols, int 
 int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream);
 
 enum { DSL_ACT_NONE = 0, DSL_ACT_SWIGLU = 1 };
+enum { DSL_OUT_NVFP4 = 3 };   /* a value of dsl_epilogue.out_dtype besides DSL_F32 / DSL_BF16 */
 
 /* Epilogue description shared by the GEMM entry points.
  *   out = acc * scale_a * scale_b [* row_scale[m]] [* col_scale[g*N+n]]
@@ -111,6 +112,15 @@ typedef struct {
                                    the fully scaled values, silu(x) = x / (1 + exp(-x)); ldc >= N/2.  Fuses the
                                    reference's swiglu (cuda/activations/fused_gated_activations.cu:27-29,75-90) into
                                    the epilogue of the gate/up projection. */
+    void* out_sf;               /* out_dtype == DSL_OUT_NVFP4 only: the result (after the activation, if any) is
+                                   quantised in the epilogue exactly as dsl_quant_fp4 would quantise it with the global
+                                   scale given here: C receives packed e2m1 bytes [M_total, Nout/2] (row pitch ldc/2
+                                   bytes, ldc % 16 == 0, Nout % 16 == 0) and out_sf the scale tiles (dsl_sf_bytes /
+                                   dsl_sf_bytes_grouped; zero-filled by the caller, rows of a ragged group start fresh
+                                   tiles as for A).  The next GEMM can consume C / out_sf as its A / sfa directly.
+                                   Served by dsl_gemm_fp4, dsl_gemm_fp8 and dsl_gemm_bf16 (not the group-scaled FP8 GEMM). */
+    float out_gs_host;          /* global scale of the quantised result ... */
+    const float* out_gs_dev;    /* ... overridden by this device scalar when non-NULL */
 } dsl_epilogue;
 
 /*
