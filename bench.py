@@ -51,6 +51,10 @@ WORKLOADS = {
                                       act="swiglu", out="nvfp4"),
     "moe_fp8_groupwise_swiglu": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
                                      act="swiglu"),
+    # the whole MoE feed-forward layer around the two grouped GEMMs (router, plan, quantise once, dispatch,
+    # gate/up GEMM with SwiGLU and NVFP4 result, down GEMM, combine); 0.01 = calibrated hidden global scale
+    "moe_layer_nvfp4": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
+                            hidden_gs=0.01),
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
 }
 DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
@@ -118,6 +122,8 @@ def build_workload(name, rank, world, device, sets, strong=False):
     cfg = WORKLOADS[name]
     kind = cfg["kind"]
     g = torch.Generator(device=device).manual_seed(1234 + rank)
+    if cfg.get("layer"):
+        return build_layer_workload(cfg, rank, world, device, sets, strong, g)
     offs = None
     if cfg.get("moe"):
         experts = cfg["experts"]          # weak scaling keeps 64 local experts (and their routed rows) per GPU
@@ -165,8 +171,35 @@ def build_workload(name, rank, world, device, sets, strong=False):
                 moe=bool(cfg.get("moe")), act=cfg.get("act"), out=cfg.get("out"))
 
 
+def build_layer_workload(cfg, rank, world, device, sets, strong, g):
+    """Whole MoE layer.  Weak scaling: every rank owns a full set of experts and its own tokens; strong
+    scaling: the experts of one layer are split over the ranks, tokens replicated, partial results all-reduced."""
+    from dsl_tool_b200 import MoEWeights, moe_forward
+    T, E, k, K, H, D = cfg["tokens"], cfg["experts"], cfg["topk"], cfg["K"], cfg["H"], cfg["D"]
+    acts, logits, wts = [], [], []
+    for s in range(sets):
+        gen = torch.Generator(device=device).manual_seed(77 + s + (0 if strong else 1000 * rank))
+        acts.append(torch.randn((T, K), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16))
+        logits.append(torch.randn((T, E), generator=gen, device=device, dtype=torch.float32))
+        w1 = (torch.randn((E, 2 * H, K), generator=gen, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
+        w2 = (torch.randn((E, D, H), generator=gen, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
+        wts.append(MoEWeights.pack(w1, w2, cfg["kind"], rank=rank if strong else 0, world=world if strong else 1,
+                                   hidden_global_scale=cfg.get("hidden_gs")))
+        del w1, w2
+    torch.cuda.synchronize()
+
+    def step(i, a=None):
+        return moe_forward(acts[i % sets] if a is None else a, logits[i % sets], wts[i % sets], k, out_dtype=torch.bfloat16)
+
+    flops = 2.0 * T * k * (2 * H * K + D * H) / (world if strong else 1)
+    return dict(step=step, acts=acts, wts=wts, offs=None, M=T * k, K=K, N=2 * H, kind=cfg["kind"], flops=flops, moe=True,
+                act="swiglu", out=None, layer=True, out_cols=D, out_rows=T)
+
+
 def split_step(wl):
     """(quantise, gemm) closures so the GEMM launch can be bracketed by its own events."""
+    if wl.get("layer"):
+        return (lambda i: None), (lambda i, q: wl["step"](i))
     from dsl_tool_b200 import quantize_fp4, quantize_fp8
     from dsl_tool_b200 import gemm_kernels as GK
     kind, offs, sets = wl["kind"], wl["offs"], len(wl["acts"])
@@ -357,7 +390,10 @@ def main():
         h.copy_(wl["acts"][j % len(wl["acts"])])
     dev_a = torch.empty_like(wl["acts"][0])
     out_cols = wl["N"] // 2 if wl.get("act") else wl["N"]
-    if wl.get("out") == "nvfp4":
+    if wl.get("layer"):
+        out_cols = wl["out_cols"]
+        host_out = torch.empty((wl["out_rows"], out_cols), dtype=torch.bfloat16).pin_memory()
+    elif wl.get("out") == "nvfp4":
         host_out = torch.empty((wl["M"], out_cols // 2), dtype=torch.uint8).pin_memory()
     else:
         host_out = torch.empty((wl["M"], out_cols), dtype=torch.bfloat16).pin_memory()
@@ -428,7 +464,7 @@ def main():
                 "ms_per_step": e2e_ms},
         # kernels of this library per step: quantiser passes + one GEMM kernel (NVFP4 tensors of up to
         # 2^18 elements are quantised by a single launch, larger ones by an amax pass + a quantise pass)
-        "gpu_launches": K_steps * ({"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
+        "gpu_launches": K_steps * 9 if wl.get("layer") else K_steps * ({"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
                                     "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]
                                    + (1 if (decode and wl["M"] > 32) else 0)),   # split-K reduction of the tiled kernel
         "cuda_graph": bool(args.graph),

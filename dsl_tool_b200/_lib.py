@@ -75,6 +75,11 @@ _SIGNATURES = {
                                          ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_quant_fp4_ref32": (_i, [_vp, _i, _ll, _vp, _vp, _vp]),
     "dsl_gemm_fp4_ref32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dsl_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "dsl_moe_plan": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "dsl_moe_dispatch_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "dsl_moe_dispatch_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _ll, _i, _i, _vp, _vp]),
+    "dsl_moe_combine": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),
 }

@@ -1,0 +1,211 @@
+"""Mixture-of-experts layer around the grouped GEMM: router top-k, expert-sorted dispatch, the two
+expert projections and the weighted combine, single GPU or expert-parallel.
+
+The reference has the grouped GEMM only (cuda/gemm/grouped_gemm.cu:79-104, registered
+triton/gemm/gemm_kernels.py:164-182); a layer that uses it needs the steps on either side, which
+live here.  Data flow of `moe_forward` (NVFP4 weights):
+
+    logits --route--> ids, weights --plan--> offsets, tile0, dest          (all on the GPU, no host sync)
+    x --quantise ONCE per token--> packed rows + scale tiles --dispatch--> expert-sorted packed rows
+      --grouped GEMM (gate/up, fused SwiGLU, result quantised in the epilogue)--> --grouped GEMM (down)-->
+      --combine (weights, slot order)--> out [tokens, d_model]
+
+Expert parallelism: every rank sees all tokens and the full routing (the router is cheap), dispatches and
+computes only its contiguous range of experts (`sharding.expert_ranges`), and the per-rank partial results
+are summed with one all-reduce - there is no token all-to-all and no host-side knowledge of the row counts.
+Buffers for the routed rows are sized for the worst case of the local experts, tokens * k rows.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .gemm_kernels import gemm_fp4_quantized, gemm_fp8_quantized, linear
+from .quantize import PackedWeight, pack_weight, quantize_fp4, quantize_fp8
+from .sharding import expert_ranges
+
+
+@dataclass
+class MoEPlan:
+    ids: torch.Tensor        # [tokens, k] int32: chosen experts
+    weights: torch.Tensor    # [tokens, k] fp32
+    offsets: torch.Tensor    # [experts + 1] int32: rows per expert, prefix sums
+    tile0: torch.Tensor      # [experts + 1] int32: prefix sums of ceil(rows / 128)
+    dest: torch.Tensor       # [tokens * k] int32: expert-sorted row of entry token * k + slot
+    experts: int
+
+
+def route(logits: torch.Tensor, k: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax over the experts and top-k: (ids [T, k] int32, weights [T, k] fp32); ties go to the lower index."""
+    dev = _lib.require_cuda(logits)
+    if logits.dim() != 2 or logits.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("logits must be [tokens, experts] float32 or bfloat16")
+    logits = logits.contiguous()
+    T, E = logits.shape
+    ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+    w = torch.empty((T, k), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_moe_route(logits.data_ptr(), _lib.dtype_code(logits.dtype), T, E, k, 1 if renormalize else 0,
+                                      ids.data_ptr(), w.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_moe_route")
+    return ids, w
+
+
+def plan(ids: torch.Tensor, weights: torch.Tensor, experts: int) -> MoEPlan:
+    """Expert-sorted row plan of the routing (stable: within an expert, rows keep token / slot order)."""
+    dev = _lib.require_cuda(ids, weights)
+    if ids.dtype != torch.int32 or ids.dim() != 2:
+        raise TypeError("ids must be [tokens, k] int32")
+    ids = ids.contiguous()
+    n = ids.numel()
+    counts = torch.empty(experts, dtype=torch.int32, device=dev)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    tile0 = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    dest = torch.empty(n, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_moe_plan(ids.data_ptr(), n, experts, counts.data_ptr(), offsets.data_ptr(), tile0.data_ptr(),
+                                     dest.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_moe_plan")
+    return MoEPlan(ids, weights.contiguous(), offsets, tile0, dest, experts)
+
+
+def _local_offsets(p: MoEPlan, first: int, last: int) -> torch.Tensor:
+    return (p.offsets[first:last + 1] - p.offsets[first]).contiguous()
+
+
+def dispatch_fp4(p: MoEPlan, packed: torch.Tensor, sf: torch.Tensor, K: int, format: str, first: int, last: int):
+    """Packed rows / scale tiles of tokens quantised once -> (expert-sorted packed rows [T*k, K/2], scale tiles in
+    the ragged-group layout) for the experts [first, last).  Rows beyond the local total stay unwritten."""
+    dev = _lib.require_cuda(packed, sf)
+    T, k = p.ids.shape
+    rows = T * k
+    nblk = K // 16 if format == "nvfp4" else K // 32
+    q_out = torch.empty((rows, K // 2), dtype=torch.uint8, device=dev)
+    sf_out = torch.zeros(int(_lib.lib().dsl_sf_bytes_grouped(rows, nblk, last - first)), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_moe_dispatch_fp4(packed.data_ptr(), sf.data_ptr(), p.ids.data_ptr(), p.dest.data_ptr(),
+                                             p.offsets.data_ptr(), p.tile0.data_ptr(), T, k, K,
+                                             _lib.FP4_NV if format == "nvfp4" else _lib.FP4_MX, first, last,
+                                             q_out.data_ptr(), sf_out.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_moe_dispatch_fp4")
+    return q_out, sf_out
+
+
+def dispatch_rows(p: MoEPlan, x: torch.Tensor, first: int, last: int) -> torch.Tensor:
+    """x [tokens, K] (any dtype whose row is a multiple of 16 bytes) -> expert-sorted rows [T*k, K]."""
+    dev = _lib.require_cuda(x)
+    x = x.contiguous()
+    T, k = p.ids.shape
+    out = torch.empty((T * k, x.shape[1]), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_moe_dispatch_rows(x.data_ptr(), p.ids.data_ptr(), p.dest.data_ptr(), p.offsets.data_ptr(), T, k,
+                                              x.shape[1] * x.element_size(), first, last, out.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_moe_dispatch_rows")
+    return out
+
+
+def combine(p: MoEPlan, y: torch.Tensor, first: int, last: int, out_dtype=torch.float32) -> torch.Tensor:
+    """y [rows, D] (expert-sorted results of the local experts) -> [tokens, D]: weighted sum over each token's
+    local slots, in slot order."""
+    dev = _lib.require_cuda(y)
+    if y.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("y must be float32 or bfloat16")
+    y = y.contiguous()
+    T, k = p.ids.shape
+    out = torch.empty((T, y.shape[1]), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_moe_combine(y.data_ptr(), _lib.dtype_code(y.dtype), p.ids.data_ptr(), p.dest.data_ptr(),
+                                        p.offsets.data_ptr(), p.weights.data_ptr(), T, k, y.shape[1], first, last,
+                                        out.data_ptr(), _lib.dtype_code(out_dtype), _lib.stream_ptr())
+    _lib.check(rc, "dsl_moe_combine")
+    return out
+
+
+@dataclass
+class MoEWeights:
+    """One rank's experts: gate/up projection [E_local, 2H, K] packed with the rows interleaved for the fused
+    SwiGLU, down projection [E_local, D, H]; `first` .. `last` is the rank's range of global expert indices."""
+    gate_up: PackedWeight
+    down: PackedWeight
+    first: int
+    last: int
+    experts: int              # global number of experts
+    hidden_global_scale: Optional[float] = None   # NVFP4: calibrated global scale of the hidden activation
+
+    @staticmethod
+    def pack(w_gate_up: torch.Tensor, w_down: torch.Tensor, format: str = "nvfp4", rank: int = 0, world: int = 1,
+             hidden_global_scale: Optional[float] = None) -> "MoEWeights":
+        """w_gate_up [E, 2H, K] ([gate; up] rows), w_down [E, D, H]: keeps and packs this rank's expert range.
+        NVFP4 global scales and per-tensor FP8 scales are those of the whole tensors, so every sharding quantises
+        identically."""
+        E = w_gate_up.shape[0]
+        first, last = expert_ranges(E, world)[rank]
+        gs1 = gs2 = None
+        if format in ("nvfp4", "fp8"):      # per-tensor quantities come from the WHOLE tensors
+            div = 2688.0 if format == "nvfp4" else 448.0
+            gs1 = w_gate_up.abs().amax().float() / div
+            gs2 = w_down.abs().amax().float() / div
+        gu = pack_weight(w_gate_up[first:last], format, global_scale=gs1, gate_up_interleave=True)
+        dn = pack_weight(w_down[first:last], format, global_scale=gs2)
+        return MoEWeights(gu, dn, first, last, E, hidden_global_scale)
+
+
+def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True) -> torch.Tensor:
+    """This rank's share of the layer's result, fp32 [tokens, D]: the sum over the slots routed to its experts.
+    NVFP4 / MXFP4 weights take the quantise-once path; with `hidden_global_scale` set (NVFP4) the hidden
+    activation is quantised in the epilogue of the gate/up GEMM, otherwise it is written in bf16 and quantised
+    by a separate pass (which, when the rank holds only part of the experts, reads the local row count back to
+    the host once)."""
+    fmt = w.gate_up.format
+    ids, wts = route(logits, k, renormalize)
+    p = plan(ids, wts, w.experts)
+    offs = _local_offsets(p, w.first, w.last)
+    K = x.shape[1]
+    if fmt in ("nvfp4", "mxfp4"):
+        packed, sf, gs = quantize_fp4(x, fmt)
+        q_rows, sf_rows = dispatch_fp4(p, packed, sf, K, fmt, w.first, w.last)
+        common = dict(format=fmt, expert_offsets=offs, b_static=True)
+        if fmt == "nvfp4" and w.hidden_global_scale is not None:
+            hq, hsf, hgs = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
+                                              global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype="nvfp4",
+                                              out_global_scale=w.hidden_global_scale, **common)
+        else:
+            h = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
+                                   global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype=torch.bfloat16, **common)
+            n_local = h.shape[0] if (w.last - w.first) == w.experts else int(offs[-1].item())
+            hq, hsf, hgs = quantize_fp4(h[:n_local], fmt, group_offsets=offs)
+        y = gemm_fp4_quantized(hq, w.down.q, hsf, w.down.scale, n=w.down.n, global_scale_a=hgs,
+                               global_scale_b=w.down.global_scale, out_dtype=torch.bfloat16, **common)
+    elif fmt == "fp8":
+        # per-tensor scale: taken over the tokens, so that it does not depend on which experts are local;
+        # the E4M3 bytes are dispatched.  The hidden activation's scale is this rank's (valid rows only).
+        qa, sa = quantize_fp8(x, "per_tensor")
+        rows = dispatch_rows(p, qa, w.first, w.last)
+        h = gemm_fp8_quantized(rows, w.gate_up.q, sa, w.gate_up.scale, n=w.gate_up.n, expert_offsets=offs, activation="swiglu",
+                               out_dtype=torch.bfloat16, b_static=True)
+        n_local = h.shape[0] if (w.last - w.first) == w.experts else int(offs[-1].item())
+        qh, sh = quantize_fp8(h[:n_local], "per_tensor")
+        y = gemm_fp8_quantized(qh, w.down.q, sh, w.down.scale, n=w.down.n, expert_offsets=offs, out_dtype=torch.bfloat16,
+                               b_static=True)
+    else:
+        rows = dispatch_rows(p, x.to(torch.bfloat16), w.first, w.last)
+        h = linear(rows, w.gate_up, expert_offsets=offs, activation="swiglu", out_dtype=torch.bfloat16)
+        y = linear(h, w.down, expert_offsets=offs, out_dtype=torch.bfloat16)
+    return combine(p, y, w.first, w.last, out_dtype=torch.float32)
+
+
+def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
+                out_dtype=torch.float32, group=None) -> torch.Tensor:
+    """One MoE feed-forward layer: x [tokens, K], router logits [tokens, experts] -> [tokens, D].
+    When `w` covers only part of the experts the per-rank partial results are summed by one all-reduce over
+    `group` (default: the default process group of torch.distributed)."""
+    out = moe_partial(x, logits, w, k, renormalize=renormalize)
+    if (w.last - w.first) < w.experts:
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized():
+            raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")
+        dist.all_reduce(out, group=group)
+    return out if out_dtype == torch.float32 else out.to(out_dtype)

@@ -157,8 +157,8 @@ def _pack_weight_impl(w: torch.Tensor, format: str, layout: str = "nk",
     """Quantise a weight for the GEMM entry points.
 
     w is [N, K] / [G, N, K] (layout "nk") or the reference's [K, N] / [G, K, N] (layout "kn",
-    cuda/gemm/fp8_gemm.cu:29-35); it is made K-major first.  `global_scale` (NVFP4 only) fixes the
-    fp32 global scale instead of deriving it from this tensor's amax - pass the unsharded tensor's
+    cuda/gemm/fp8_gemm.cu:29-35); it is made K-major first.  `global_scale` (NVFP4: the fp32 global scale;
+    per-tensor FP8: the scale) fixes that value instead of deriving it from this tensor's amax - pass the unsharded tensor's
     amax/2688 when packing a column or expert shard so that every shard quantises exactly as the
     whole weight would.  `gate_up_interleave`: the N = 2H output rows are a fused gate/up projection
     ([gate; up], the input layout of the reference's swiglu, cuda/activations/fused_gated_activations.cu:75-90);
@@ -185,7 +185,7 @@ def _pack_weight_impl(w: torch.Tensor, format: str, layout: str = "nk",
     if format == "bf16":
         return PackedWeight("bf16", flat.to(torch.bfloat16).contiguous(), None, None, G, N, K)
     if format == "fp8":
-        q, s = quantize_fp8(flat, "per_tensor")
+        q, s = quantize_fp8(flat, "per_tensor", scale=global_scale)
         return PackedWeight("fp8", q, s, None, G, N, K)
     if format == "fp8_block128":
         if G == 1 or N % 128 == 0:

@@ -178,6 +178,34 @@ int dsl_gemm_fp4_ref32(const uint8_t* A, const uint8_t* B, float* C, const float
                        int M, int N, int K, void* stream);
 
 /*
+ * Mixture-of-experts steps either side of the grouped GEMM (the reference stops at the grouped GEMM itself,
+ * cuda/gemm/grouped_gemm.cu:79-104; these have no counterpart there).  All deterministic.
+ *   dsl_moe_route     logits [tokens, experts] (f32 / bf16) -> ids [tokens, k] (int32, ties to the lower index) and
+ *                     weights [tokens, k] = softmax probabilities of the chosen experts (renorm: divided by their sum)
+ *   dsl_moe_plan      ids -> offsets [experts+1] (rows per expert, prefix sums: the group_offsets of the GEMMs),
+ *                     tile0 [experts+1] (prefix sums of ceil(rows/128): first scale tile of each expert) and
+ *                     dest [tokens*k]: row of entry token*k+slot in the expert-sorted order (stable);
+ *                     counts_scratch: experts ints
+ *   dsl_moe_dispatch_fp4  copies the packed rows and scale bytes of tokens quantised ONCE (q_in [tokens, K/2], sf_in
+ *                     token-major scale tiles) to their expert-sorted rows for the experts [first, last): q_out
+ *                     [rows, K/2], sf_out in the ragged-group tile layout (zero-filled by the caller)
+ *   dsl_moe_dispatch_rows the same mapping for plain rows of row_bytes (% 16 == 0) bytes
+ *   dsl_moe_combine   out[t, :] = sum over t's slots with a local expert, in slot order, of weight * y[row, :]
+ */
+int dsl_moe_route(const void* logits, int dtype, int tokens, int experts, int k, int renorm, int* ids_out,
+                  float* weights_out, void* stream);
+int dsl_moe_plan(const int* ids, int entries, int experts, int* counts_scratch, int* offsets_out, int* tile0_out,
+                 int* dest_out, void* stream);
+int dsl_moe_dispatch_fp4(const uint8_t* q_in, const uint8_t* sf_in, const int* ids, const int* dest, const int* offsets,
+                         const int* tile0, int tokens, int k, int K, int format, int first_expert, int last_expert,
+                         uint8_t* q_out, uint8_t* sf_out, void* stream);
+int dsl_moe_dispatch_rows(const void* x, const int* ids, const int* dest, const int* offsets, int tokens, int k,
+                          long long row_bytes, int first_expert, int last_expert, void* out, void* stream);
+int dsl_moe_combine(const void* y, int y_dtype, const int* ids, const int* dest, const int* offsets, const float* weights,
+                    int tokens, int k, int d_model, int first_expert, int last_expert, void* out, int out_dtype,
+                    void* stream);
+
+/*
  * dsl_gemm_fp4 for callers that cannot allocate device memory (no counterpart in the
  * reference).  Same operands and result as dsl_gemm_fp4 on a dense problem, but the split-K
  * scratch is a fixed DSL_STATIC_SCRATCH_BYTES array inside the library instead of

@@ -40,6 +40,20 @@ y = ep.forward_from_global(x, offs, gather=True, out_dtype="float32")
 err = float((y - full).norm() / full.norm())
 print(rank, "expert-parallel relF", err, tuple(y.shape), flush=True)
 ok &= err < 1e-6
+# whole MoE layer, experts split over the ranks, partial results summed by all-reduce
+from dsl_tool_b200 import MoEWeights, moe_forward
+T, E, k, K, H, D = 96, 6, 2, 256, 128, 192
+xm = torch.randn(T, K, generator=g, device="cuda").bfloat16()
+lg = torch.randn(T, E, generator=g, device="cuda")
+w1 = (torch.randn(E, 2 * H, K, generator=g, device="cuda") * 0.05).bfloat16()
+w2 = (torch.randn(E, D, H, generator=g, device="cuda") * 0.05).bfloat16()
+for fmt in ("nvfp4", "bf16"):
+    hgs = 0.004 if fmt == "nvfp4" else None
+    whole = moe_forward(xm, lg, MoEWeights.pack(w1, w2, fmt, hidden_global_scale=hgs), k)
+    part = moe_forward(xm, lg, MoEWeights.pack(w1, w2, fmt, rank=rank, world=world, hidden_global_scale=hgs), k)
+    err = float((part - whole).norm() / whole.norm())
+    print(rank, fmt, "moe layer expert-parallel relF", err, flush=True)
+    ok &= err < 1e-5
 torch.cuda.synchronize()
 dist.destroy_process_group()
 sys.exit(0 if ok else 3)
