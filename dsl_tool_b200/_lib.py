@@ -76,6 +76,7 @@ _SIGNATURES = {
     "dsl_quant_fp4_ref32": (_i, [_vp, _i, _ll, _vp, _vp, _vp]),
     "dsl_gemm_fp4_ref32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dsl_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "dsl_moe_plan_scratch_bytes": (ctypes.c_size_t, [_i, _i]),
     "dsl_moe_plan": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "dsl_moe_dispatch_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "dsl_moe_dispatch_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _ll, _i, _i, _vp, _vp]),

@@ -72,54 +72,90 @@ moe_route_kernel(const T* __restrict__ logits, int tokens, int experts, int k, i
 }
 
 // ---- plan: stable sort of the (token, slot) entries by expert ---------------------------------
-// One CTA per expert walks all entries in order.  Pass `count` writes how many entries name the
-// expert; pass `place` (second launch) turns the counts into offsets and gives every entry of the
-// expert its row: offsets[e] + (number of earlier entries of e).
-__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ ids, int entries, int* __restrict__ counts) {
-    __shared__ int s_part[8];
-    const int e = blockIdx.x;
-    int c = 0;
-    for (int i = threadIdx.x; i < entries; i += 256) c += ids[i] == e;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = c;
+// Three small launches, no atomics that could decide an order:
+//   count   every CTA histograms its block of kPlanBlock consecutive entries (shared-memory counters: sums do
+//           not depend on the order of the additions) -> block_counts[block][expert]
+//   scan    one CTA: per expert the running sum over the blocks, then offsets / tile0 over the experts;
+//           block_counts becomes the first row of (block, expert)
+//   place   every CTA walks its block in order; an entry's row = first row of (block, expert) + number of
+//           earlier entries of the block with the same expert (warp match + warps committed in order)
+constexpr int kPlanBlock = 2048;
+
+__global__ void __launch_bounds__(256)
+moe_count_kernel(const int* __restrict__ ids, int entries, int experts, int* __restrict__ block_counts) {
+    extern __shared__ int s_bins[];
+    for (int e = threadIdx.x; e < experts; e += 256) s_bins[e] = 0;
+    __syncthreads();
+    const int i0 = blockIdx.x * kPlanBlock;
+    for (int i = i0 + threadIdx.x; i < min(entries, i0 + kPlanBlock); i += 256) {
+        const int e = ids[i];
+        if (e >= 0 && e < experts) atomicAdd(&s_bins[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += 256) block_counts[static_cast<size_t>(blockIdx.x) * experts + e] = s_bins[e];
+}
+
+__global__ void __launch_bounds__(1024)
+moe_scan_kernel(int* __restrict__ block_counts, int blocks, int experts, int* __restrict__ offsets, int* __restrict__ tile0) {
+    __shared__ int s_cnt[DSL_MAX_GROUPS];
+    for (int e = threadIdx.x; e < experts; e += 1024) {
+        int run = 0;
+        for (int b = 0; b < blocks; ++b) {
+            const int c = block_counts[static_cast<size_t>(b) * experts + e];
+            block_counts[static_cast<size_t>(b) * experts + e] = run;
+            run += c;
+        }
+        s_cnt[e] = run;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
-        int s = 0;
-        for (int w = 0; w < 8; ++w) s += s_part[w];
-        counts[e] = s;
+        int rows = 0, tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            const int c = s_cnt[e];
+            offsets[e] = rows;
+            tile0[e] = tiles;
+            s_cnt[e] = rows;
+            rows += c;
+            tiles += (c + 127) >> 7;
+        }
+        offsets[experts] = rows;
+        tile0[experts] = tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += 1024) {
+        const int base = s_cnt[e];
+        for (int b = 0; b < blocks; ++b) block_counts[static_cast<size_t>(b) * experts + e] += base;
     }
 }
 
 __global__ void __launch_bounds__(256)
-moe_place_kernel(const int* __restrict__ ids, int entries, int experts, const int* __restrict__ counts,
-                 int* __restrict__ offsets, int* __restrict__ tile0, int* __restrict__ dest) {
-    __shared__ int s_base;
-    __shared__ int s_warp[8];
-    const int e = blockIdx.x;
-    if (threadIdx.x == 0) {
-        int rows = 0, tiles = 0;
-        for (int j = 0; j < e; ++j) { rows += counts[j]; tiles += (counts[j] + 127) >> 7; }
-        s_base = rows;
-        offsets[e] = rows;
-        tile0[e] = tiles;
-        if (e == experts - 1) { offsets[experts] = rows + counts[e]; tile0[experts] = tiles + ((counts[e] + 127) >> 7); }
-    }
+moe_place_kernel(const int* __restrict__ ids, int entries, int experts, const int* __restrict__ block_first,
+                 int* __restrict__ dest) {
+    extern __shared__ int s_next[];                        // next free row of every expert, for this block
+    for (int e = threadIdx.x; e < experts; e += 256) s_next[e] = block_first[static_cast<size_t>(blockIdx.x) * experts + e];
     __syncthreads();
-    int running = s_base;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i0 = 0; i0 < entries; i0 += 256) {
-        const int i = i0 + threadIdx.x;
-        const bool mine = i < entries && ids[i] == e;
-        const unsigned bal = __ballot_sync(0xFFFFFFFFu, mine);
-        if (lane == 0) s_warp[warp] = __popc(bal);
-        __syncthreads();
-        int before = 0, total = 0;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) { const int c = s_warp[w]; before += w < warp ? c : 0; total += c; }
-        if (mine) dest[i] = running + before + __popc(bal & ((1u << lane) - 1u));
-        running += total;
-        __syncthreads();
+    const int i0 = blockIdx.x * kPlanBlock;
+    for (int c0 = i0; c0 < min(entries, i0 + kPlanBlock); c0 += 256) {
+        const int i = c0 + threadIdx.x;
+        const bool valid = i < entries;
+        int e = valid ? ids[i] : -1;
+        if (e < 0 || e >= experts) e = -1;                 // out-of-range ids get no row
+        const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int leader = __ffs(peers) - 1;
+        for (int w = 0; w < 8; ++w) {                      // warps commit in order: entries stay in sequence
+            if (warp == w) {
+                int base = 0;
+                if (e >= 0 && lane == leader) {
+                    base = s_next[e];
+                    s_next[e] = base + __popc(peers);
+                }
+                base = __shfl_sync(0xFFFFFFFFu, base, leader);
+                if (e >= 0) dest[i] = base + rank;
+            }
+            __syncthreads();
+        }
     }
 }
 
@@ -264,12 +300,20 @@ extern "C" int dsl_moe_route(const void* logits, int dtype, int tokens, int expe
     return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int dsl_moe_plan(const int* ids, int entries, int experts, int* counts_scratch, int* offsets_out, int* tile0_out,
+extern "C" size_t dsl_moe_plan_scratch_bytes(int entries, int experts) {
+    if (entries < 0 || experts < 1) return 0;
+    return static_cast<size_t>((entries + kPlanBlock - 1) / kPlanBlock + 1) * static_cast<size_t>(experts) * sizeof(int);
+}
+
+extern "C" int dsl_moe_plan(const int* ids, int entries, int experts, int* scratch, int* offsets_out, int* tile0_out,
                             int* dest_out, void* stream) {
-    if (ids == nullptr || counts_scratch == nullptr || offsets_out == nullptr || tile0_out == nullptr || dest_out == nullptr) return DSL_ERR_NULL;
+    if (ids == nullptr || scratch == nullptr || offsets_out == nullptr || tile0_out == nullptr || dest_out == nullptr) return DSL_ERR_NULL;
     if (entries < 0 || experts < 1 || experts > DSL_MAX_GROUPS) return DSL_ERR_SHAPE;
-    moe_count_kernel<<<experts, 256, 0, st_of(stream)>>>(ids, entries, counts_scratch);
-    moe_place_kernel<<<experts, 256, 0, st_of(stream)>>>(ids, entries, experts, counts_scratch, offsets_out, tile0_out, dest_out);
+    const int blocks = (entries + kPlanBlock - 1) / kPlanBlock;
+    const size_t smem = static_cast<size_t>(experts) * sizeof(int);
+    if (blocks > 0) moe_count_kernel<<<blocks, 256, smem, st_of(stream)>>>(ids, entries, experts, scratch);
+    moe_scan_kernel<<<1, 1024, 0, st_of(stream)>>>(scratch, blocks, experts, offsets_out, tile0_out);
+    if (blocks > 0) moe_place_kernel<<<blocks, 256, smem, st_of(stream)>>>(ids, entries, experts, scratch, dest_out);
     return static_cast<int>(cudaGetLastError());
 }
 

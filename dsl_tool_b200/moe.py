@@ -61,7 +61,7 @@ def plan(ids: torch.Tensor, weights: torch.Tensor, experts: int) -> MoEPlan:
         raise TypeError("ids must be [tokens, k] int32")
     ids = ids.contiguous()
     n = ids.numel()
-    counts = torch.empty(experts, dtype=torch.int32, device=dev)
+    counts = torch.empty(int(_lib.lib().dsl_moe_plan_scratch_bytes(n, experts)) // 4, dtype=torch.int32, device=dev)
     offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
     tile0 = torch.empty(experts + 1, dtype=torch.int32, device=dev)
     dest = torch.empty(n, dtype=torch.int32, device=dev)

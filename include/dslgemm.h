@@ -185,7 +185,7 @@ int dsl_gemm_fp4_ref32(const uint8_t* A, const uint8_t* B, float* C, const float
  *   dsl_moe_plan      ids -> offsets [experts+1] (rows per expert, prefix sums: the group_offsets of the GEMMs),
  *                     tile0 [experts+1] (prefix sums of ceil(rows/128): first scale tile of each expert) and
  *                     dest [tokens*k]: row of entry token*k+slot in the expert-sorted order (stable);
- *                     counts_scratch: experts ints
+ *                     scratch: dsl_moe_plan_scratch_bytes(entries, experts) bytes
  *   dsl_moe_dispatch_fp4  copies the packed rows and scale bytes of tokens quantised ONCE (q_in [tokens, K/2], sf_in
  *                     token-major scale tiles) to their expert-sorted rows for the experts [first, last): q_out
  *                     [rows, K/2], sf_out in the ragged-group tile layout (zero-filled by the caller)
@@ -194,7 +194,8 @@ int dsl_gemm_fp4_ref32(const uint8_t* A, const uint8_t* B, float* C, const float
  */
 int dsl_moe_route(const void* logits, int dtype, int tokens, int experts, int k, int renorm, int* ids_out,
                   float* weights_out, void* stream);
-int dsl_moe_plan(const int* ids, int entries, int experts, int* counts_scratch, int* offsets_out, int* tile0_out,
+size_t dsl_moe_plan_scratch_bytes(int entries, int experts);
+int dsl_moe_plan(const int* ids, int entries, int experts, int* scratch, int* offsets_out, int* tile0_out,
                  int* dest_out, void* stream);
 int dsl_moe_dispatch_fp4(const uint8_t* q_in, const uint8_t* sf_in, const int* ids, const int* dest, const int* offsets,
                          const int* tile0, int tokens, int k, int K, int format, int first_expert, int last_expert,
