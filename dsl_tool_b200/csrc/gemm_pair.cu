@@ -317,21 +317,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int row = ti.row0 + 128 * static_cast<int>(rank) + quad * 32 + lane;
             const bool row_ok = row < ti.row_end;
             const float rs = (row_ok && args.row_scale != nullptr) ? args.row_scale[row] : 1.0f;
+            // Two chunk buffers: the tensor-memory load of the next 32 columns is in flight while the current
+            // ones are scaled, converted and stored (a short-K tile's MMAs are no longer than its epilogue).
+            // block-scaled kinds: the 64 columns shared with the other accumulator go first
+            const uint32_t t_row = tmem_base + acc * C::ACC1_COL + (static_cast<uint32_t>(quad * 32) << 16);
+            const bool rot = C::SF_ATOMS > 0 && acc == 0;
+            uint32_t va[32], vb[32];
+            tmem_ld_32x32b_x32(t_row + (rot ? 6 : 0) * 32, va);
 #pragma unroll 1
-            for (int j = 0; j < pr::TILE_N / 32; ++j) {
-                // block-scaled kinds: the 64 columns shared with the other accumulator go first
-                const int c = (C::SF_ATOMS > 0 && acc == 0) ? ((j + 6) & 7) : j;
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + acc * C::ACC1_COL + c * 32 + (static_cast<uint32_t>(quad * 32) << 16), v);
+            for (int j = 0; j < pr::TILE_N / 32; j += 2) {
+                const int ca = rot ? ((j + 6) & 7) : j;
+                const int cb = rot ? ((j + 7) & 7) : j + 1;
                 tmem_ld_wait();
-                if (C::SF_ATOMS > 0 && j == 1) {
+                tmem_ld_32x32b_x32(t_row + cb * 32, vb);
+                if (row_ok && ti.n0 + ca * 32 < args.n)
+                    store_chunk32(args, row, ti.n0 + ca * 32, ti.group, va, s1, s2, rs, vec_ok, ti.sf_tile + static_cast<int>(rank), quad * 32 + lane);
+                tmem_ld_wait();
+                if (C::SF_ATOMS > 0 && j == 0) {       // chunks 0 and 1 of this walk (the shared columns) are in registers
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(ovl_free, 0);
                 }
-                const int col0 = ti.n0 + c * 32;
-                if (row_ok && col0 < args.n)
-                    store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok, ti.sf_tile + static_cast<int>(rank), quad * 32 + lane);
+                if (j + 2 < pr::TILE_N / 32) tmem_ld_32x32b_x32(t_row + (rot ? ((j + 8) & 7) : j + 2) * 32, va);
+                if (row_ok && ti.n0 + cb * 32 < args.n)
+                    store_chunk32(args, row, ti.n0 + cb * 32, ti.group, vb, s1, s2, rs, vec_ok, ti.sf_tile + static_cast<int>(rank), quad * 32 + lane);
             }
             tc_fence_before();
             __syncwarp();
