@@ -42,9 +42,13 @@ __device__ __forceinline__ void store_nvfp4_block(const GemmArgs& args, int row,
 // v: 32 fp32 accumulators (bit patterns) of row `row`, columns col0..col0+31 of group `group`.
 // out = (acc * s1) * s2 [* row_scale[row]] [* col_scale[group*n + col]]
 // sf_tile / rin: only read when the result is quantised (args.out_sf != nullptr).
-__device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int col0, int group,
-                                              const uint32_t (&v)[32], float s1, float s2, float rs, bool vec_ok,
-                                              int sf_tile = 0, int rin = 0) {
+// FULL = false compiles the activation and quantisation branches out: the group-scaled FP8 kernels hold 128
+// accumulators per thread and must not pay registers (measured: spills in the promotion loop) for paths they
+// take rarely; they are instantiated once without and once with those branches and the launcher chooses.
+template <bool FULL>
+__device__ __forceinline__ void store_chunk32_t(const GemmArgs& args, int row, int col0, int group,
+                                                const uint32_t (&v)[32], float s1, float s2, float rs, bool vec_ok,
+                                                int sf_tile = 0, int rin = 0) {
     float f[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -58,7 +62,7 @@ __device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int
         for (int i = 0; i < 32; ++i)
             if (col0 + i < args.n) f[i] = __fmul_rn(f[i], cs[col0 + i]);
     }
-    if (args.act == DSL_ACT_SWIGLU) {
+    if (FULL && args.act == DSL_ACT_SWIGLU) {
         // columns (2j, 2j+1) = (gate_j, up_j) -> output column col0/2 + j of an [m, n/2] result;
         // silu(x) = x / (1 + exp(-x)) as cuda/activations/fused_gated_activations.cu:27-29, in fp32
         float o[16];
@@ -103,7 +107,7 @@ __device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int
         }
         return;
     }
-    if (args.out_sf != nullptr) {         // n is a multiple of 16: one or two whole blocks in this chunk
+    if (FULL && args.out_sf != nullptr) {         // n is a multiple of 16: one or two whole blocks in this chunk
         const float gs = args.out_gs_dev != nullptr ? *args.out_gs_dev : args.out_gs;
         if (col0 < args.n) store_nvfp4_block(args, row, col0, f, gs, sf_tile, rin);
         if (col0 + 16 < args.n) store_nvfp4_block(args, row, col0 + 16, f + 16, gs, sf_tile, rin);
@@ -137,6 +141,12 @@ __device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int
             }
         }
     }
+}
+
+__device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int col0, int group,
+                                              const uint32_t (&v)[32], float s1, float s2, float rs, bool vec_ok,
+                                              int sf_tile = 0, int rin = 0) {
+    store_chunk32_t<true>(args, row, col0, group, v, s1, s2, rs, vec_ok, sf_tile, rin);
 }
 
 }  // namespace dsl

@@ -42,7 +42,7 @@ constexpr int THREADS = 320;
 static_assert(SMEM_BYTES > 116224 && SMEM_BYTES <= 232448, "one CTA per SM");
 }  // namespace gw
 
-template <bool SB_BLOCK>
+template <bool SB_BLOCK, bool ACT>
 __global__ void __launch_bounds__(gw::THREADS, 1)
 gemm_fp8_groupwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const GemmArgs args) {
@@ -203,7 +203,7 @@ gemm_fp8_groupwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 uint32_t v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(acc[c * 32 + i]);
-                store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
+                store_chunk32_t<ACT>(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
             }
         }
     }
@@ -234,7 +234,7 @@ static int sm_count_gw() {
     return n;
 }
 
-template <bool SB_BLOCK>
+template <bool SB_BLOCK, bool ACT>
 static int launch_gw(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
     CUtensorMap ta, tb;
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
@@ -242,7 +242,7 @@ static int launch_gw(const void* A, const void* B, const GemmArgs& args, cudaStr
     if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, gw::BLOCK_N)) return DSL_ERR_DRIVER;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_kernel<SB_BLOCK>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_kernel<SB_BLOCK, ACT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, gw::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
         attr_set = true;
@@ -251,7 +251,7 @@ static int launch_gw(const void* A, const void* B, const GemmArgs& args, cudaStr
     const long long max_tiles = m_tiles_max * ((args.n + gw::BLOCK_N - 1) / gw::BLOCK_N);
     long long grid = max_tiles < sm_count_gw() ? max_tiles : sm_count_gw();
     if (grid < 1) grid = 1;
-    gemm_fp8_groupwise_kernel<SB_BLOCK><<<static_cast<unsigned>(grid), gw::THREADS, gw::SMEM_BYTES, st>>>(ta, tb, args);
+    gemm_fp8_groupwise_kernel<SB_BLOCK, ACT><<<static_cast<unsigned>(grid), gw::THREADS, gw::SMEM_BYTES, st>>>(ta, tb, args);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -261,7 +261,10 @@ int launch_gemm_fp8_groupwise(const void* A, const void* B, GemmArgs args, cudaS
     const bool force_1cta = forced != nullptr && strcmp(forced, "1cta") == 0;
     if (!force_1cta && args.m_total > 128 && args.n >= 256) return launch_gemm_fp8_groupwise_pair(A, B, args, st);
     if (args.band <= 0) args.band = 8;
-    return args.sb_block ? launch_gw<true>(A, B, args, st) : launch_gw<false>(A, B, args, st);
+    // two instantiations: the plain epilogue keeps the promotion loop free of spills, the activation one is larger
+    if (args.act != DSL_ACT_NONE)
+        return args.sb_block ? launch_gw<true, true>(A, B, args, st) : launch_gw<false, true>(A, B, args, st);
+    return args.sb_block ? launch_gw<true, false>(A, B, args, st) : launch_gw<false, false>(A, B, args, st);
 }
 
 }  // namespace dsl

@@ -72,7 +72,7 @@ struct Walker {
 
 }  // namespace gwp
 
-template <bool SB_BLOCK>
+template <bool SB_BLOCK, bool ACT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gwp::THREADS, 1)
 gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                                const GemmArgs args) {
@@ -277,7 +277,7 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 uint32_t v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(acc[c * 32 + i]);
-                store_chunk32(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
+                store_chunk32_t<ACT>(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
             }
         }
     }
@@ -298,7 +298,7 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     }
 }
 
-template <bool SB_BLOCK>
+template <bool SB_BLOCK, bool ACT>
 static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
     CUtensorMap ta, tb;
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
@@ -306,7 +306,7 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, 128)) return DSL_ERR_DRIVER;
     static int max_clusters = 0;
     if (max_clusters == 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_pair_kernel<SB_BLOCK>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, gwp::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
         int dev = 0, sms = 0;
@@ -317,7 +317,7 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
         cfg.blockDim = dim3(gwp::THREADS);
         cfg.dynamicSmemBytes = gwp::SMEM_BYTES;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_fp8_groupwise_pair_kernel<SB_BLOCK>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>, &cfg);
         max_clusters = (e == cudaSuccess && n > 0) ? n : (sms > 1 ? sms / 2 : 1);
         (void)cudaGetLastError();
     }
@@ -325,14 +325,17 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     const long long max_tiles = m_tiles_max * ((args.n + gwp::TILE_N - 1) / gwp::TILE_N);
     long long clusters = max_tiles < max_clusters ? max_tiles : max_clusters;
     if (clusters < 1) clusters = 1;
-    gemm_fp8_groupwise_pair_kernel<SB_BLOCK><<<static_cast<unsigned>(2 * clusters), gwp::THREADS, gwp::SMEM_BYTES, st>>>(ta, tb, args);
+    gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT><<<static_cast<unsigned>(2 * clusters), gwp::THREADS, gwp::SMEM_BYTES, st>>>(ta, tb, args);
     return static_cast<int>(cudaGetLastError());
 }
 
 int launch_gemm_fp8_groupwise_pair(const void* A, const void* B, GemmArgs args, cudaStream_t st) {
     if (args.m_total <= 0 || args.n <= 0) return 0;
     if (args.band <= 0) args.band = 8;
-    return args.sb_block ? launch_gw_pair<true>(A, B, args, st) : launch_gw_pair<false>(A, B, args, st);
+    // two instantiations: the plain epilogue keeps the promotion loop free of spills, the activation one is larger
+    if (args.act != DSL_ACT_NONE)
+        return args.sb_block ? launch_gw_pair<true, true>(A, B, args, st) : launch_gw_pair<false, true>(A, B, args, st);
+    return args.sb_block ? launch_gw_pair<true, false>(A, B, args, st) : launch_gw_pair<false, false>(A, B, args, st);
 }
 
 }  // namespace dsl
