@@ -313,24 +313,45 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmArgs args,
     const size_t slice = static_cast<size_t>(args.m_total) * args.n;
     const float* p = args.partial + static_cast<size_t>(row) * args.n + col0;
     const bool vec = args.n % 4 == 0;
-    for (int ks = 0; ks < split_k; ++ks, p += slice) {
-        if (vec) {
-            const float4 v = *reinterpret_cast<const float4*>(p);
-            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
-        } else {
+    if (vec) {
+        // all slices' loads are issued before the first addition (split_k <= 8): the partial sums are L2 hits
+        // whose latency, one after the other, used to be most of this kernel's time
+        float4 v[8];
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+            v[ks] = ks < split_k ? __ldcg(reinterpret_cast<const float4*>(p + ks * slice)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            if (ks < split_k) { acc[0] += v[ks].x; acc[1] += v[ks].y; acc[2] += v[ks].z; acc[3] += v[ks].w; }
+        }
+    } else {
+        for (int ks = 0; ks < split_k; ++ks, p += slice)
             for (int i = 0; i < 4; ++i)
                 if (col0 + i < args.n) acc[i] += p[i];
-        }
     }
     const float rs = args.row_scale != nullptr ? args.row_scale[row] : 1.0f;
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        x[i] = __fmul_rn(__fmul_rn(acc[i], s1), s2);
+        if (args.row_scale != nullptr) x[i] = __fmul_rn(x[i], rs);
+        if (args.col_scale != nullptr && col0 + i < args.n) x[i] = __fmul_rn(x[i], args.col_scale[col0 + i]);
+    }
+    const size_t off = static_cast<size_t>(row) * args.ldc + col0;
+    if (vec && args.ldc % 4 == 0) {
+        if (args.out_bf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]), hi = __floats2bfloat162_rn(x[2], x[3]);
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(args.c) + off) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        } else {
+            *reinterpret_cast<float4*>(static_cast<float*>(args.c) + off) = make_float4(x[0], x[1], x[2], x[3]);
+        }
+        return;
+    }
     for (int i = 0; i < 4; ++i) {
         if (col0 + i >= args.n) break;
-        float x = __fmul_rn(__fmul_rn(acc[i], s1), s2);
-        if (args.row_scale != nullptr) x = __fmul_rn(x, rs);
-        if (args.col_scale != nullptr) x = __fmul_rn(x, args.col_scale[col0 + i]);
-        const size_t off = static_cast<size_t>(row) * args.ldc + col0 + i;
-        if (args.out_bf16) static_cast<__nv_bfloat16*>(args.c)[off] = __float2bfloat16_rn(x);
-        else static_cast<float*>(args.c)[off] = x;
+        if (args.out_bf16) static_cast<__nv_bfloat16*>(args.c)[off + i] = __float2bfloat16_rn(x[i]);
+        else static_cast<float*>(args.c)[off + i] = x[i];
     }
 }
 

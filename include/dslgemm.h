@@ -89,6 +89,7 @@ enum { DSL_OUT_NVFP4 = 3 };   /* a value of dsl_epilogue.out_dtype besides DSL_F
 /* Epilogue description shared by the GEMM entry points.
  *   out = acc * scale_a * scale_b [* row_scale[m]] [* col_scale[g*N+n]]
  * scale_x is *scale_x_dev when that pointer is non-NULL, else scale_x_host.
+ * Zero the struct before filling it in: every field added after `workspace_bytes` means "off" when 0 / NULL.
  * With a workspace, dense problems with at most 128 rows go to the weight-streaming kernel (all SMs
  * stream equal shares of B; shared tiles are summed in ascending K order), and other dense problems
  * that would occupy less than half of the SMs are cut along K into up to 8 slices summed in order. */
