@@ -19,7 +19,7 @@ LIB_PATH = os.environ.get("DSLGEMM_LIBRARY", os.path.join(_HERE, "libdslgemm.so"
 F32, BF16, F16 = 0, 1, 2
 FP8_PER_TENSOR, FP8_GROUP_1X128, FP8_BLOCK_128X128 = 0, 1, 2
 FP4_NV, FP4_MX = 0, 1
-ACT_NONE, ACT_SWIGLU = 0, 1
+ACT_NONE, ACT_SWIGLU, ACT_GEGLU = 0, 1, 2
 OUT_NVFP4 = 3
 MAX_GROUPS = 1024
 STATIC_SCRATCH_BYTES = 4 << 20

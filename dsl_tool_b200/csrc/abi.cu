@@ -76,8 +76,8 @@ static int fill_common(GemmArgs& a, const void* A, const void* B, void* C, long 
                        long long k_bytes, const int* group_offsets, int groups, const dsl_epilogue* ep,
                        uint32_t* status) {
     if (A == nullptr || B == nullptr || C == nullptr || ep == nullptr) return DSL_ERR_NULL;
-    if (ep->activation != DSL_ACT_NONE && ep->activation != DSL_ACT_SWIGLU) return DSL_ERR_ENUM;
-    const bool glu = ep->activation == DSL_ACT_SWIGLU;
+    if (ep->activation != DSL_ACT_NONE && ep->activation != DSL_ACT_SWIGLU && ep->activation != DSL_ACT_GEGLU) return DSL_ERR_ENUM;
+    const bool glu = ep->activation != DSL_ACT_NONE;
     if (glu && N % 2 != 0) return DSL_ERR_SHAPE;
     if (M_total < 0 || N < 0 || k_bytes <= 0 || M_total > 0x7FFFFFFFll || ldc < (glu ? N / 2 : N)) return DSL_ERR_SHAPE;
     if (k_bytes % 16 != 0) return DSL_ERR_SHAPE;

@@ -62,15 +62,18 @@ __device__ __forceinline__ void store_chunk32_t(const GemmArgs& args, int row, i
         for (int i = 0; i < 32; ++i)
             if (col0 + i < args.n) f[i] = __fmul_rn(f[i], cs[col0 + i]);
     }
-    if (FULL && args.act == DSL_ACT_SWIGLU) {
+    if (FULL && args.act != DSL_ACT_NONE) {
         // columns (2j, 2j+1) = (gate_j, up_j) -> output column col0/2 + j of an [m, n/2] result;
-        // silu(x) = x / (1 + exp(-x)) as cuda/activations/fused_gated_activations.cu:27-29, in fp32
+        // SwiGLU: silu(x) = x / (1 + exp(-x)) (cuda/activations/fused_gated_activations.cu:27-29).
+        // GeGLU: gelu(x) = 0.5 x (1 + tanh(c (x + k x^3))) (:32-37) = x / (1 + exp(-2c (x + k x^3))), the same shape.
+        const bool geglu = args.act == DSL_ACT_GEGLU;
         float o[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float g = f[2 * j];
+            const float z = geglu ? 1.5957691216f * (g + 0.044715f * g * g * g) : g;
             // fast exponential and division (a few ulp): the epilogue must stay shorter than a tile's MMAs
-            o[j] = __fmul_rn(__fdividef(g, 1.0f + __expf(-g)), f[2 * j + 1]);
+            o[j] = __fmul_rn(__fdividef(g, 1.0f + __expf(-z)), f[2 * j + 1]);
         }
         const int c0 = col0 >> 1;
         if (args.out_sf != nullptr) {     // n/2 is a multiple of 16 here, so the 16 outputs are one whole block

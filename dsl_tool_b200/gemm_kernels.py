@@ -41,14 +41,16 @@ def _activation_code(activation: Optional[str]) -> int:
         return _lib.ACT_NONE
     if activation == "swiglu":
         return _lib.ACT_SWIGLU
-    raise ValueError(f"activation must be None or 'swiglu', got {activation!r}")
+    if activation == "geglu":
+        return _lib.ACT_GEGLU
+    raise ValueError(f"activation must be None, 'swiglu' or 'geglu', got {activation!r}")
 
 
 def _out_cols(n: int, activation: Optional[str]) -> int:
     """Columns of the result: n, or n/2 when (gate, up) column pairs are folded by the epilogue."""
-    if _activation_code(activation) == _lib.ACT_SWIGLU:
+    if _activation_code(activation) != _lib.ACT_NONE:
         if n % 2:
-            raise ValueError("activation 'swiglu' needs an even number of GEMM columns")
+            raise ValueError("a gated activation needs an even number of GEMM columns")
         return n // 2
     return n
 
@@ -264,13 +266,13 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
     """a [M, K] high-precision activations x packed weight -> [M, N]: quantise the activations
     in the weight's format (one pass on the GPU) and run the matching GEMM.  The packed weight is
     treated as complete (the activation quantiser always sits between its producer and the GEMM).
-    activation "swiglu": the weight is a fused gate/up projection packed with `gate_up_interleave=True`;
-    the result is [M, N/2] = silu(gate) * up, computed in the GEMM epilogue
+    activation "swiglu" / "geglu": the weight is a fused gate/up projection packed with `gate_up_interleave=True`;
+    the result is [M, N/2] = silu(gate) * up (gelu(gate) * up, tanh form), computed in the GEMM epilogue
     (cuda/activations/fused_gated_activations.cu:75-90 without the [M, N] round trip through memory).
     out_dtype "nvfp4" (with `out_global_scale`): the result is quantised in the same epilogue and returned as
     (packed bytes, scale tiles, global scale), the A operand of a following `gemm_fp4_quantized`."""
-    if _activation_code(activation) == _lib.ACT_SWIGLU and not w.gate_up_interleaved:
-        raise ValueError("activation 'swiglu' needs a weight packed with gate_up_interleave=True")
+    if _activation_code(activation) != _lib.ACT_NONE and not w.gate_up_interleaved:
+        raise ValueError("a gated activation needs a weight packed with gate_up_interleave=True")
     if a.dim() != 2 or a.shape[1] != w.k:
         raise ValueError(f"activations must be [M, {w.k}], got {tuple(a.shape)}")
     if w.groups > 1 and expert_offsets is None:
@@ -467,7 +469,7 @@ def grouped_gemm(A: torch.Tensor, B, num_groups: Optional[int] = None, expert_of
     first, the input layout of the reference's swiglu); the result has H columns, silu(gate) * up, computed
     in the GEMM epilogue.  A PackedWeight passed as B must have been packed with `gate_up_interleave=True`.
     """
-    glu = _activation_code(activation) == _lib.ACT_SWIGLU
+    glu = _activation_code(activation) != _lib.ACT_NONE
     formats = {"bf16": "bf16", "fp8": "fp8", "fp8_groupwise": "fp8_block128", "nvfp4": "nvfp4", "mxfp4": "mxfp4"}
     if format not in formats:
         raise ValueError(f"format must be one of {sorted(formats)}, got {format!r}")

@@ -83,7 +83,7 @@ int dsl_quant_fp4(const void* x, int dtype, long long rows, long long cols, int 
  * (cuda/gemm/fp8_gemm.cu:29-35, B[k*N+n]) into the K-major [N, K] the tensor cores read. */
 int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream);
 
-enum { DSL_ACT_NONE = 0, DSL_ACT_SWIGLU = 1 };
+enum { DSL_ACT_NONE = 0, DSL_ACT_SWIGLU = 1, DSL_ACT_GEGLU = 2 };
 enum { DSL_OUT_NVFP4 = 3 };   /* a value of dsl_epilogue.out_dtype besides DSL_F32 / DSL_BF16 */
 
 /* Epilogue description shared by the GEMM entry points.
@@ -107,12 +107,13 @@ typedef struct {
                                    kernel is launched with programmatic stream serialisation and then starts
                                    fetching B while that predecessor (e.g. the activation quantiser) still runs;
                                    A, its scales and every output are touched only after the predecessor is done. */
-    int activation;             /* DSL_ACT_NONE, or DSL_ACT_SWIGLU: the GEMM's columns are (gate, up) pairs - column 2j
+    int activation;             /* DSL_ACT_NONE, or DSL_ACT_SWIGLU / DSL_ACT_GEGLU: the GEMM's columns are (gate, up) pairs - column 2j
                                    is gate_j, column 2j+1 is up_j, i.e. the weight rows were interleaved when it was
                                    packed - and C is [M_total, N/2] with C[m,j] = silu(gate) * up computed in fp32 on
                                    the fully scaled values, silu(x) = x / (1 + exp(-x)); ldc >= N/2.  Fuses the
                                    reference's swiglu (cuda/activations/fused_gated_activations.cu:27-29,75-90) into
-                                   the epilogue of the gate/up projection. */
+                                   the epilogue of the gate/up projection.  GEGLU: gelu(gate) * up with the tanh form
+                                   of the same file (:32-37, :92-105). */
     void* out_sf;               /* out_dtype == DSL_OUT_NVFP4 only: the result (after the activation, if any) is
                                    quantised in the epilogue exactly as dsl_quant_fp4 would quantise it with the global
                                    scale given here: C receives packed e2m1 bytes [M_total, Nout/2] (row pitch ldc/2

@@ -40,6 +40,24 @@ def _swiglu_of_interleaved(full):
     return (g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * u
 
 
+def _geglu_of_interleaved(full):       # the reference's gelu, tanh form (fused_gated_activations.cu:32-37)
+    g, u = full[:, 0::2].astype(np.float64), full[:, 1::2].astype(np.float64)
+    return (0.5 * g * (1.0 + np.tanh(0.7978845608 * (g + 0.044715 * g ** 3))) * u).astype(np.float32)
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "fp8_block128", "bf16"])
+@pytest.mark.parametrize("M", [5, 300])
+def test_dense_geglu(cuda_device, fmt, M):
+    rng = np.random.default_rng(M)
+    H, K = 192, 512
+    a = torch.from_numpy(activations(rng, M, K, outliers=True)).bfloat16()
+    w = torch.from_numpy(weights(rng, 2 * H, K, std=0.05)).bfloat16()
+    pw = D.pack_weight(w.cuda(), fmt, gate_up_interleave=True)
+    got = D.linear(a.cuda(), pw, activation="geglu")
+    want = _geglu_of_interleaved(_oracle_gemm(fmt, a.float().numpy(), _interleave(w.float().numpy())))
+    assert tuple(got.shape) == (M, H) and rel_frobenius(got.cpu().numpy(), want) <= REL_FROB_TOL
+
+
 @pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "fp8", "fp8_block128", "bf16"])
 @pytest.mark.parametrize("M,H", [(5, 192), (300, 192), (77, 100), (300, 328)])
 def test_dense_swiglu(cuda_device, fmt, M, H):
