@@ -342,16 +342,60 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                     if (epilogue_sync() && warp == 2 && lane == 0)
                         bulk_send_to_cta(recv + static_cast<size_t>(crank) * (TOK * 128), recv, C::PART_BYTES, recv_bar, 0);
                 } else if (ok) {
-                    const float cs = (col_ok && args.col_scale != nullptr) ? args.col_scale[col] : 1.0f;
-                    if (mbar_wait(recv_bar, 0, abort_flag, ST_TIMEOUT_EPILOGUE) && col_ok) {
+                    // leader: every thread finishes 8 consecutive columns of a row (16 threads per row, 8 rows per
+                    // pass): 16-byte reads of the staged tiles and one 16-byte store per row piece instead of a
+                    // 2-byte store per element, which is what the tail of this kernel used to wait for
+                    const bool staged = epilogue_sync();                       // own tile is in shared memory
+                    if (staged && mbar_wait(recv_bar, 0, abort_flag, ST_TIMEOUT_EPILOGUE)) {
                         const int runs = plan.cluster_runs;
-#pragma unroll 4
-                        for (int r = 0; r < args.m_total; ++r) {      // a few rows in flight, still a short body
-                            const float* src = recv + r * 128 + nl;
-                            float sum = src[0];
+                        const int et = (warp - 2) * 32 + lane;
+                        const int g8 = (et & 15) * 8;
+                        const int colg = tile * 128 + g8;
+                        float cs8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            cs8[j] = (args.col_scale != nullptr && colg + j < args.n) ? args.col_scale[colg + j] : 1.0f;
+                        const bool vec = colg + 8 <= args.n && (args.out_bf16 ? args.ldc % 8 == 0 : args.ldc % 4 == 0);
 #pragma unroll 1
-                            for (int p = 1; p < runs; ++p) sum += src[p * (TOK * 128)];   // ascending K
-                            store_out(args, r, col, sum, s1, s2, cs);
+                        for (int r = et >> 4; r < args.m_total; r += 8) {
+                            const float4* src = reinterpret_cast<const float4*>(recv + r * 128 + g8);
+                            float4 a = src[0], b = src[1];
+#pragma unroll 1
+                            for (int p = 1; p < runs; ++p) {                   // ascending K
+                                const float4 pa = src[p * (TOK * 32)], pb = src[p * (TOK * 32) + 1];
+                                a.x += pa.x; a.y += pa.y; a.z += pa.z; a.w += pa.w;
+                                b.x += pb.x; b.y += pb.y; b.z += pb.z; b.w += pb.w;
+                            }
+                            float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                            const float rs = args.row_scale != nullptr ? args.row_scale[r] : 1.0f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                x[j] = __fmul_rn(__fmul_rn(x[j], s1), s2);
+                                if (args.row_scale != nullptr) x[j] = __fmul_rn(x[j], rs);
+                                if (args.col_scale != nullptr) x[j] = __fmul_rn(x[j], cs8[j]);
+                            }
+                            const size_t off = static_cast<size_t>(r) * args.ldc + colg;
+                            if (vec && args.out_bf16) {
+                                uint32_t w4[4];
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+                                    w4[j] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.c) + off) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                            } else if (vec) {
+                                float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.c) + off);
+                                dst[0] = make_float4(x[0], x[1], x[2], x[3]);
+                                dst[1] = make_float4(x[4], x[5], x[6], x[7]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    if (colg + j < args.n) {
+                                        if (args.out_bf16) static_cast<__nv_bfloat16*>(args.c)[off + j] = __float2bfloat16_rn(x[j]);
+                                        else static_cast<float*>(args.c)[off + j] = x[j];
+                                    }
+                                }
+                            }
                         }
                     }
                 }
