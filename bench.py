@@ -465,8 +465,7 @@ def main():
         # kernels of this library per step: quantiser passes + one GEMM kernel (NVFP4 tensors of up to
         # 2^18 elements are quantised by a single launch, larger ones by an amax pass + a quantise pass)
         "gpu_launches": K_steps * 9 if wl.get("layer") else K_steps * ({"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
-                                    "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]
-                                   + (1 if (decode and wl["M"] > 32) else 0)),   # split-K reduction of the tiled kernel
+                                    "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]),
         "cuda_graph": bool(args.graph),
         "clocks": clocks,
     }

@@ -436,7 +436,8 @@ static int launch_one(const void* A, const void* B, const GemmArgs& args, long l
 
 // Which kernel serves a problem: the CTA-pair kernel (256x256 tiles) once there is more than
 // one 128-row tile of work and the output is at least 256 wide; the 1-CTA kernel otherwise.
-// Dense problems with at most DSL_DECODE_MAX_ROWS activation rows go to the weight-streaming kernel.
+// Dense problems with at most DSL_DECODE_MAX_ROWS activation rows go to the weight-streaming kernel when it
+// serves them (launch_gemm_decode says so).
 // DSLGEMM_KERNEL=1cta|pair|decode overrides the choice (for measurements).
 static int forced_kernel() {
     static int v = []() {

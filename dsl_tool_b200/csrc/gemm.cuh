@@ -45,7 +45,7 @@ struct GemmArgs {
     uint32_t* status;
 };
 
-constexpr int DSL_DECODE_MAX_ROWS = 32;    // activation rows the weight-streaming kernel (gemm_decode.cu) takes
+constexpr int DSL_DECODE_MAX_ROWS = 128;   // activation rows the weight-streaming kernel (gemm_decode.cu) takes
 constexpr int DSL_NOT_SERVED = -1000;      // launch_gemm_decode: problem outside its domain, use the tiled kernels
 
 int launch_gemm_decode(int kind, const void* A, const void* B, const GemmArgs& args, cudaStream_t st);

@@ -2,7 +2,7 @@
 // bound by reading the weight once from HBM, so the kernel is organised around that stream.
 //
 //   * Operand roles are swapped: the WEIGHT tile (128 rows of B, i.e. 128 output columns) is the
-//     M = 128 side of tcgen05.mma and the activations (TOK = 16 or 32 rows of A, zero-filled beyond
+//     M = 128 side of tcgen05.mma and the activations (TOK = 16 ... 128 rows of A, zero-filled beyond
 //     m_total by the TMA unit) are the N = TOK side.  The accumulator is 128 lanes x TOK columns,
 //     so an MMA costs in proportion to the real token count instead of a padded 128-row tile.
 //   * Work is cut along K so that every SM streams a share of the weight: the (column tile,
@@ -45,19 +45,22 @@ struct DecCfg {
     static constexpr int SF_STAGE = SF_ATOMS * 512;
     static constexpr int STAGE_BYTES = W_STAGE + X_STAGE + 2 * SF_STAGE;
     // cluster mode: room for this CTA's own fp32 partial tile ([TOK][128], slot 0) and those of up to
-    // MAX_PEERS peers (slots 1..)
+    // MAX_PEERS peers (slots 1..).  Up to 32 tokens it is a region of its own; beyond that the tiles are too
+    // large for one and the drained operand ring is reused (the leader tells its peers when its ring is free).
     static constexpr int PART_BYTES = TOK * 128 * 4;
-    static constexpr int MAX_PEERS = 3;
-    static constexpr int RECV_BYTES = (MAX_PEERS + 1) * PART_BYTES;
+    static constexpr bool STAGE_IN_RING = TOK > 32;
+    static constexpr int RECV_BYTES = STAGE_IN_RING ? 0 : 4 * PART_BYTES;
     static constexpr int RING_BUDGET = 200 * 1024 - RECV_BYTES;
     static constexpr int NUM_STAGES = RING_BUDGET / STAGE_BYTES > 10 ? 10 : RING_BUDGET / STAGE_BYTES;
+    static constexpr int MAX_PEERS = STAGE_IN_RING ? ((NUM_STAGES * STAGE_BYTES) / PART_BYTES >= 4 ? 3 : 1) : 3;
+    static_assert(!STAGE_IN_RING || (MAX_PEERS + 1) * PART_BYTES <= NUM_STAGES * STAGE_BYTES, "partial tiles must fit the ring");
     static constexpr int OFF_W = 0;
     static constexpr int OFF_X = OFF_W + NUM_STAGES * W_STAGE;
     static constexpr int OFF_SFW = OFF_X + NUM_STAGES * X_STAGE;
     static constexpr int OFF_SFX = OFF_SFW + NUM_STAGES * SF_STAGE;
-    static constexpr int OFF_RECV = OFF_SFX + NUM_STAGES * SF_STAGE;          // 1024-byte aligned
-    static constexpr int OFF_BAR = OFF_RECV + RECV_BYTES;
-    static constexpr int NUM_BARS = 2 * NUM_STAGES + 6;
+    static constexpr int OFF_RECV = STAGE_IN_RING ? 0 : OFF_SFX + NUM_STAGES * SF_STAGE;          // 1024-byte aligned
+    static constexpr int OFF_BAR = OFF_SFX + NUM_STAGES * SF_STAGE + RECV_BYTES;
+    static constexpr int NUM_BARS = 2 * NUM_STAGES + 7;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
     static constexpr int OFF_TABLE = OFF_MISC + 16;                          // first unit of every CTA (+ the end)
     static constexpr int SMEM_BYTES = OFF_TABLE + (DEC_MAX_CTAS + 2) * 4 + 1024;
@@ -148,6 +151,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     uint64_t* acc_empty = acc_full + 2;
     uint64_t* epi_bar = acc_empty + 2;     // meeting point of the four epilogue warps (bounded, like every wait here)
     uint64_t* recv_bar = epi_bar + 1;      // cluster mode, leader: completes when every peer's partial tile has landed
+    uint64_t* go_bar = recv_bar + 1;       // cluster mode, peers, ring staging: the leader's ring is free to receive
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 4);
     volatile uint32_t* last_flag = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_MISC + 8);
@@ -164,6 +168,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         for (int i = 0; i < 2; ++i) { mbar_init(acc_full + i, 1); mbar_init(acc_empty + i, 4); }
         mbar_init(epi_bar, 4);
         mbar_init(recv_bar, 1);
+        mbar_init(go_bar, 1);
         *abort_flag = 0;
         fence_mbar_init();
         if (clustered && crank == 0) mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>(plan.cluster_runs - 1) * C::PART_BYTES);
@@ -336,10 +341,18 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                     }
                     tc_fence_before();
                 }
+                if (C::STAGE_IN_RING && ok && crank == 0) {
+                    // this CTA's MMAs are done (acc_full), so its operand ring can take the peers' tiles
+                    __syncwarp();
+                    if (warp == 2 && lane == 0)
+                        for (int p = 1; p < plan.cluster_runs; ++p) mbar_arrive_cluster(go_bar, static_cast<uint32_t>(p));
+                }
                 if (ok && crank != 0) {
                     // peer: own partial tile (slot 0 here) -> the leader's slot for this rank, one bulk copy
                     fence_proxy_async_smem();
-                    if (epilogue_sync() && warp == 2 && lane == 0)
+                    bool go = epilogue_sync();
+                    if (C::STAGE_IN_RING && go) go = mbar_wait_cluster(go_bar, 0, abort_flag, ST_TIMEOUT_EPILOGUE);
+                    if (go && warp == 2 && lane == 0)
                         bulk_send_to_cta(recv + static_cast<size_t>(crank) * (TOK * 128), recv, C::PART_BYTES, recv_bar, 0);
                 } else if (ok) {
                     // leader: every thread finishes 8 consecutive columns of a row (16 threads per row, 8 rows per
@@ -566,6 +579,9 @@ static int launch_decode_one(const void* A, const void* B, const GemmArgs& args,
     if (ctas > plan.units / 4) { ctas = plan.units / 4; cluster_runs = 0; }
     if (forced_ctas > 0 && forced_ctas <= plan.units) ctas = forced_ctas;
     if (ctas > DEC_MAX_CTAS) { ctas = DEC_MAX_CTAS; cluster_runs = 0; }
+    // More than 32 tokens: only the cluster combine is fast enough (the scratch combine walks the rows with
+    // one L2 round trip after the other); otherwise the tiled split-K kernel takes the problem.
+    if (TOK > 32 && cluster_runs == 0) return DSL_NOT_SERVED;
     if (cluster_runs == 0) {
         const size_t words_bytes = static_cast<size_t>(plan.n_tiles) * sizeof(unsigned long long);
         const size_t per_cta = 2ull * TOK * 128 * sizeof(float);
@@ -613,10 +629,11 @@ static int launch_decode_one(const void* A, const void* B, const GemmArgs& args,
 
 template <int KIND>
 static int launch_decode_kind(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
-    // Beyond 32 rows the tiled split-K kernel is as fast (measured at N = K = 8192: 64 rows 17 vs 15 us).
-    static_assert(DSL_DECODE_MAX_ROWS == 32, "one instantiation per token bucket");
+    static_assert(DSL_DECODE_MAX_ROWS == 128, "one instantiation per token bucket");
     if (args.m_total <= 16) return launch_decode_one<KIND, 16>(A, B, args, st);
-    return launch_decode_one<KIND, 32>(A, B, args, st);
+    if (args.m_total <= 32) return launch_decode_one<KIND, 32>(A, B, args, st);
+    if (args.m_total <= 64) return launch_decode_one<KIND, 64>(A, B, args, st);
+    return launch_decode_one<KIND, 128>(A, B, args, st);
 }
 
 // Returns DSL_NOT_SERVED when the problem is not one this kernel serves (the caller then uses the tiled kernels).

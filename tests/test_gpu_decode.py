@@ -1,7 +1,8 @@
-"""The weight-streaming kernel for decode shapes (at most 32 activation rows, one row group; more
-rows take the tiled split-K kernel, covered by the same cases): operand roles swapped, K cut into
-runs whose fp32 partial tiles are summed in ascending K order - inside a thread-block cluster
-through shared memory when a tile has 2 or 4 runs, through scratch otherwise.
+"""The weight-streaming kernel for decode shapes (at most 128 activation rows, one row group; beyond
+32 rows only where the cluster combine applies, else the tiled split-K kernel, covered by the same
+cases): operand roles swapped, K cut into runs whose fp32 partial tiles are summed in ascending K
+order - inside a thread-block cluster through shared memory when a tile has 2 or 4 runs, through
+scratch otherwise.
 Same oracle and tolerance as the tiled kernels (relative Frobenius <= 1e-3 on the fp32 result)."""
 import numpy as np
 import pytest
@@ -29,8 +30,7 @@ def _oracle(fmt, ao, wo):
     return ao @ wo.T
 
 
-# both token buckets of the streaming kernel (16 / 32 accumulator columns), the hand-over to the tiled
-# kernel above 32 rows, and both sides of each boundary
+# every token bucket of the streaming kernel (16 / 32 / 64 / 128 accumulator columns) and both sides of each boundary
 @pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "fp8", "bf16"])
 @pytest.mark.parametrize("M", [1, 16, 17, 32, 33, 64, 65, 128])
 def test_token_buckets(cuda_device, fmt, M):
@@ -66,7 +66,8 @@ def test_ragged_edges(cuda_device, fmt, N, K, M):
 # one case per way of cutting the work: clusters of 4 and of 2 runs per tile, whole tiles (no cut),
 # and runs that cross tile borders (more column tiles than SMs)
 @pytest.mark.parametrize("fmt", ["nvfp4", "fp8"])
-@pytest.mark.parametrize("N,K,M", [(2304, 4096, 16), (6400, 4096, 9), (12800, 1024, 16), (19200, 2048, 5), (19200, 2048, 30)])
+@pytest.mark.parametrize("N,K,M", [(2304, 4096, 16), (6400, 4096, 9), (12800, 1024, 16), (19200, 2048, 5), (19200, 2048, 30),
+                                   (2304, 4096, 64), (6400, 4096, 128), (19200, 2048, 100)])
 def test_work_split_modes(cuda_device, fmt, N, K, M):
     from dsl_tool_b200 import _lib, pack_weight
     from dsl_tool_b200.gemm_kernels import linear
