@@ -152,4 +152,49 @@ __device__ __forceinline__ void store_chunk32(const GemmArgs& args, int row, int
     store_chunk32_t<true>(args, row, col0, group, v, s1, s2, rs, vec_ok, sf_tile, rin);
 }
 
+// Plain bf16 result, stored by the whole warp: every lane scales and converts its own row's 32 columns
+// (64 bytes), the 32 rows are exchanged through 2 KB of shared memory (16-byte pieces, XOR-placed so that
+// neither side has bank conflicts), and every store instruction then writes 8 rows x 64 contiguous bytes
+// instead of 16 bytes in each of 32 rows - a quarter of the memory transactions.  Short-K tiles, whose MMAs
+// are no longer than their epilogue, are where this shows (MoE down projection).  Call with all 32 lanes;
+// rows at or beyond row_end are not written.
+__device__ __forceinline__ void store_chunk32_bf16_warp(const GemmArgs& args, uint8_t* scratch, int row_base, int row_end,
+                                                        int col0, int group, const uint32_t (&v)[32], float s1, float s2,
+                                                        float rs, int lane) {
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float x = __fmul_rn(__fmul_rn(__uint_as_float(v[i]), s1), s2);
+        if (args.row_scale != nullptr) x = __fmul_rn(x, rs);
+        f[i] = x;
+    }
+    if (args.col_scale != nullptr) {
+        const float* cs = args.col_scale + static_cast<size_t>(group) * args.n;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = __fmul_rn(f[i], cs[col0 + i]);
+    }
+    const int swz = (lane >> 1) & 3;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[8 * p + 2 * j], f[8 * p + 2 * j + 1]);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(scratch + lane * 64 + 16 * (p ^ swz)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __syncwarp();
+    const int p = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int rr = (lane >> 2) + 8 * i;
+        const uint4 d = *reinterpret_cast<const uint4*>(scratch + rr * 64 + 16 * (p ^ ((rr >> 1) & 3)));
+        const int row = row_base + rr;
+        if (row < row_end)
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.c) + static_cast<size_t>(row) * args.ldc + col0 + 8 * p) = d;
+    }
+    __syncwarp();
+}
+
 }  // namespace dsl

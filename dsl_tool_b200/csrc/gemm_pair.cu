@@ -52,7 +52,8 @@ struct Cfg {
     static constexpr int NUM_BARS = 3 * NUM_STAGES + 2 * ACC_STAGES + 1;
     static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
     static constexpr int OFF_TABLE = OFF_MISC + 16;                         // offs, tile0, sftile0
-    static constexpr int SMEM_BYTES = OFF_TABLE + 3 * (DSL_MAX_GROUPS + 1) * 4 + 1024;
+    static constexpr int OFF_EPI = (OFF_TABLE + 3 * (DSL_MAX_GROUPS + 1) * 4 + 15) & ~15;   // 4 epilogue warps x 2 KB exchange
+    static constexpr int SMEM_BYTES = OFF_EPI + 4 * 2048 + 1024;
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared-memory limit");
     static_assert(SMEM_BYTES > 116224, "two CTAs could share an SM and deadlock on tensor-memory allocation");
 };
@@ -306,6 +307,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         float s2 = args.s2_dev != nullptr ? *args.s2_dev : args.s2;
         if (args.scale_product) { s1 = s1 * s2; s2 = 1.0f; }
         const bool vec_ok = args.out_bf16 ? (args.ldc % 8 == 0) : (args.ldc % 4 == 0);
+        // plain bf16 results leave through the warp-wide store (rows exchanged in shared memory)
+        const bool warp_store = args.out_bf16 && vec_ok && args.act == DSL_ACT_NONE && args.out_sf == nullptr;
+        uint8_t* epi_scratch = smem + C::OFF_EPI + (warp - 2) * 2048;
         bool ok = true;
         long long iter = 0;
         for (long long t = pair_id; t < tw.total && ok; t += num_pairs, ++iter) {
@@ -321,6 +325,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // ones are scaled, converted and stored (a short-K tile's MMAs are no longer than its epilogue).
             // block-scaled kinds: the 64 columns shared with the other accumulator go first
             const uint32_t t_row = tmem_base + acc * C::ACC1_COL + (static_cast<uint32_t>(quad * 32) << 16);
+            const int row_warp = ti.row0 + 128 * static_cast<int>(rank) + quad * 32;
             const bool rot = C::SF_ATOMS > 0 && acc == 0;
             uint32_t va[32], vb[32];
             tmem_ld_32x32b_x32(t_row + (rot ? 6 : 0) * 32, va);
@@ -330,7 +335,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int cb = rot ? ((j + 7) & 7) : j + 1;
                 tmem_ld_wait();
                 tmem_ld_32x32b_x32(t_row + cb * 32, vb);
-                if (row_ok && ti.n0 + ca * 32 < args.n)
+                if (warp_store && ti.n0 + ca * 32 + 32 <= args.n)
+                    store_chunk32_bf16_warp(args, epi_scratch, row_warp, ti.row_end, ti.n0 + ca * 32, ti.group, va, s1, s2, rs, lane);
+                else if (row_ok && ti.n0 + ca * 32 < args.n)
                     store_chunk32(args, row, ti.n0 + ca * 32, ti.group, va, s1, s2, rs, vec_ok, ti.sf_tile + static_cast<int>(rank), quad * 32 + lane);
                 tmem_ld_wait();
                 if (C::SF_ATOMS > 0 && j == 0) {       // chunks 0 and 1 of this walk (the shared columns) are in registers
@@ -339,7 +346,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (lane == 0) mbar_arrive_cluster(ovl_free, 0);
                 }
                 if (j + 2 < pr::TILE_N / 32) tmem_ld_32x32b_x32(t_row + (rot ? ((j + 8) & 7) : j + 2) * 32, va);
-                if (row_ok && ti.n0 + cb * 32 < args.n)
+                if (warp_store && ti.n0 + cb * 32 + 32 <= args.n)
+                    store_chunk32_bf16_warp(args, epi_scratch, row_warp, ti.row_end, ti.n0 + cb * 32, ti.group, vb, s1, s2, rs, lane);
+                else if (row_ok && ti.n0 + cb * 32 < args.n)
                     store_chunk32(args, row, ti.n0 + cb * 32, ti.group, vb, s1, s2, rs, vec_ok, ti.sf_tile + static_cast<int>(rank), quad * 32 + lane);
             }
             tc_fence_before();
