@@ -189,11 +189,13 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
     torch.cuda.synchronize()
 
     def step(i, a=None):
-        return moe_forward(acts[i % sets] if a is None else a, logits[i % sets], wts[i % sets], k, out_dtype=torch.bfloat16)
+        # expert-parallel ranks exchange bf16 partial results and keep their own token rows (reduce-scatter)
+        return moe_forward(acts[i % sets] if a is None else a, logits[i % sets], wts[i % sets], k, out_dtype=torch.bfloat16,
+                           reduce="reduce_scatter", exchange_dtype=torch.bfloat16)
 
     flops = 2.0 * T * k * (2 * H * K + D * H) / (world if strong else 1)
     return dict(step=step, acts=acts, wts=wts, offs=None, M=T * k, K=K, N=2 * H, kind=cfg["kind"], flops=flops, moe=True,
-                act="swiglu", out=None, layer=True, out_cols=D, out_rows=T)
+                act="swiglu", out=None, layer=True, out_cols=D, out_rows=T // (world if strong else 1))
 
 
 def split_step(wl):

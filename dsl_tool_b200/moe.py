@@ -198,14 +198,29 @@ def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
 
 
 def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
-                out_dtype=torch.float32, group=None) -> torch.Tensor:
+                out_dtype=torch.float32, group=None, reduce: str = "all_reduce", exchange_dtype=None) -> torch.Tensor:
     """One MoE feed-forward layer: x [tokens, K], router logits [tokens, experts] -> [tokens, D].
-    When `w` covers only part of the experts the per-rank partial results are summed by one all-reduce over
-    `group` (default: the default process group of torch.distributed)."""
+    When `w` covers only part of the experts the per-rank partial results are summed over `group` (default: the
+    default process group of torch.distributed): reduce "all_reduce" leaves the whole result on every rank,
+    "reduce_scatter" leaves rank r with token rows [r * tokens / world, (r + 1) * tokens / world) - half the
+    traffic, and what a sequence-sharded consumer wants.  `exchange_dtype` (e.g. torch.bfloat16) rounds the
+    partial results before they travel; default fp32."""
+    if reduce not in ("all_reduce", "reduce_scatter"):
+        raise ValueError("reduce must be 'all_reduce' or 'reduce_scatter'")
     out = moe_partial(x, logits, w, k, renormalize=renormalize)
     if (w.last - w.first) < w.experts:
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized():
             raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")
-        dist.all_reduce(out, group=group)
-    return out if out_dtype == torch.float32 else out.to(out_dtype)
+        if exchange_dtype is not None and exchange_dtype != out.dtype:
+            out = out.to(exchange_dtype)
+        if reduce == "all_reduce":
+            dist.all_reduce(out, group=group)
+        else:
+            world = dist.get_world_size(group)
+            if out.shape[0] % world:
+                raise ValueError(f"reduce_scatter needs the token count ({out.shape[0]}) to be a multiple of the group size ({world})")
+            shard = torch.empty((out.shape[0] // world, out.shape[1]), dtype=out.dtype, device=out.device)
+            dist.reduce_scatter_tensor(shard, out, group=group)
+            out = shard
+    return out if out.dtype == out_dtype else out.to(out_dtype)

@@ -54,6 +54,13 @@ for fmt in ("nvfp4", "bf16"):
     err = float((part - whole).norm() / whole.norm())
     print(rank, fmt, "moe layer expert-parallel relF", err, flush=True)
     ok &= err < 1e-5
+    shard = moe_forward(xm, lg, MoEWeights.pack(w1, w2, fmt, rank=rank, world=world, hidden_global_scale=hgs), k,
+                        reduce="reduce_scatter", exchange_dtype=torch.bfloat16)
+    rows = T // world
+    ref = whole[rank * rows:(rank + 1) * rows]
+    err = float((shard - ref).norm() / ref.norm())
+    print(rank, fmt, "moe layer reduce-scatter (bf16 exchange) relF", err, tuple(shard.shape), flush=True)
+    ok &= err < 1e-2 and tuple(shard.shape) == (rows, D)
 torch.cuda.synchronize()
 dist.destroy_process_group()
 sys.exit(0 if ok else 3)
