@@ -180,3 +180,18 @@ def test_expert_parallel_partials_add_up(cuda_device, fmt):
         assert rel < 0.05, rel
     else:
         assert torch.allclose(parts[0] + parts[1], whole, rtol=1e-5, atol=1e-6)
+
+
+def test_token_permutation_invariance_at_scale(cuda_device):
+    """Size-independent property of the whole layer: permuting the tokens permutes the result rows and changes
+    nothing else (a row's value depends only on the token, its experts and the fixed summation orders)."""
+    rng = np.random.default_rng(50)
+    T, E, k, K, H, Dm = 4096, 64, 8, 1024, 512, 1024
+    x, logits, w1, w2 = _layer_inputs(rng, T, E, K, H, Dm, cuda_device)
+    wts = D.MoEWeights.pack(w1, w2, "nvfp4", hidden_global_scale=0.004)
+    perm = torch.from_numpy(rng.permutation(T)).to(cuda_device)
+    base = D.moe_forward(x, logits, wts, k)
+    again = D.moe_forward(x[perm].contiguous(), logits[perm].contiguous(), wts, k)
+    _lib.check_status()
+    assert torch.equal(again, base[perm])
+    assert torch.isfinite(base).all() and float(base.abs().max()) > 0
