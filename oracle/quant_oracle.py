@@ -376,3 +376,48 @@ def rel_frobenius(got, want) -> float:
     want = np.asarray(want, dtype=np.float64)
     den = np.linalg.norm(want)
     return float(np.linalg.norm(got - want) / den) if den > 0 else float(np.linalg.norm(got - want))
+
+
+# ---- gated activations (consumers of the gate/up projection) ---------------------------------
+
+def silu(x) -> np.ndarray:
+    """x / (1 + exp(-x)) in fp32 (cuda/activations/fused_gated_activations.cu:27-29;
+    tilelang/activations/activation_kernels.py:58-59 writes it x * sigmoid(x))."""
+    x = _f32(x)
+    return (x / (F32(1) + np.exp(-x, dtype=F32))).astype(F32)
+
+
+def gelu_tanh(x) -> np.ndarray:
+    """0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) (fused_gated_activations.cu:32-37), evaluated in
+    fp64 and rounded once."""
+    x = _f32(x).astype(np.float64)
+    return (0.5 * x * (1.0 + np.tanh(0.7978845608 * (x + 0.044715 * x ** 3)))).astype(F32)
+
+
+def swiglu(x) -> np.ndarray:
+    """[B, 2H] with the gate in the first H columns -> [B, H] = silu(gate) * up
+    (fused_gated_activations.cu:75-90, triton/activations/activation_kernels.py:105-115)."""
+    x = _f32(x)
+    h = x.shape[-1] // 2
+    return (silu(x[..., :h]) * x[..., h:]).astype(F32)
+
+
+def geglu(x) -> np.ndarray:
+    """[B, 2H] -> [B, H] = gelu_tanh(gate) * up (fused_gated_activations.cu:92-105)."""
+    x = _f32(x)
+    h = x.shape[-1] // 2
+    return (gelu_tanh(x[..., :h]) * x[..., h:]).astype(F32)
+
+
+def interleave_gate_up(w) -> np.ndarray:
+    """Weight rows [.., 2H, K] ordered [gate; up] -> gate_0, up_0, gate_1, up_1, ... (the order the fused epilogue wants)."""
+    w = np.asarray(w)
+    h = w.shape[-2] // 2
+    return np.stack((w[..., :h, :], w[..., h:, :]), axis=-2).reshape(w.shape)
+
+
+def gated_of_interleaved(full, kind: str = "swiglu") -> np.ndarray:
+    """The same activations on a projection whose columns are (gate, up) pairs."""
+    full = _f32(full)
+    g, u = full[..., 0::2], full[..., 1::2]
+    return ((silu(g) if kind == "swiglu" else gelu_tanh(g)) * u).astype(F32)

@@ -9,31 +9,14 @@ import torch
 import dsl_tool_b200 as D
 from dsl_tool_b200 import _lib, moe
 from dsl_tool_b200.gemm_kernels import gemm_fp4_quantized
+from oracle import moe_oracle as MO
 from tests.helpers import activations
 
 pytestmark = pytest.mark.gpu
 
 
-def _route_np(logits, k, renorm):
-    l = logits.astype(np.float32)
-    p = np.exp(l - l.max(1, keepdims=True), dtype=np.float32)
-    p = p / p.sum(1, keepdims=True, dtype=np.float32)
-    ids = np.argsort(-l, axis=1, kind="stable")[:, :k].astype(np.int32)      # ties: lower index first
-    w = np.take_along_axis(p, ids, 1)
-    if renorm:
-        w = w / w.sum(1, keepdims=True, dtype=np.float32)
-    return ids, w
-
-
-def _plan_np(ids, experts):
-    flat = ids.reshape(-1)
-    counts = np.bincount(flat, minlength=experts)
-    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
-    tile0 = np.concatenate([[0], np.cumsum((counts + 127) // 128)]).astype(np.int32)
-    order = np.argsort(flat, kind="stable")
-    dest = np.empty_like(flat)
-    dest[order] = np.arange(flat.size, dtype=flat.dtype)
-    return offsets, tile0, dest.astype(np.int32)
+_route_np = lambda logits, k, renorm: MO.route(logits, k, renorm)
+_plan_np = MO.plan
 
 
 @pytest.mark.parametrize("T,E,k", [(1, 8, 2), (257, 64, 8), (100, 200, 5), (64, 1000, 32)])

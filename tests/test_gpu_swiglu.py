@@ -13,9 +13,7 @@ from tests.helpers import BF16_REL_FROB_TOL, REL_FROB_TOL, activations, moe_offs
 pytestmark = pytest.mark.gpu
 
 
-def _interleave(w):                     # [.., 2H, K] with gate rows first -> gate_0, up_0, gate_1, up_1, ...
-    h = w.shape[-2] // 2
-    return np.stack((w[..., :h, :], w[..., h:, :]), axis=-2).reshape(w.shape)
+_interleave = O.interleave_gate_up
 
 
 def _oracle_gemm(fmt, ao, wo):
@@ -35,14 +33,8 @@ def _oracle_gemm(fmt, ao, wo):
     return ao @ wo.T
 
 
-def _swiglu_of_interleaved(full):
-    g, u = full[:, 0::2].astype(np.float32), full[:, 1::2].astype(np.float32)
-    return (g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * u
-
-
-def _geglu_of_interleaved(full):       # the reference's gelu, tanh form (fused_gated_activations.cu:32-37)
-    g, u = full[:, 0::2].astype(np.float64), full[:, 1::2].astype(np.float64)
-    return (0.5 * g * (1.0 + np.tanh(0.7978845608 * (g + 0.044715 * g ** 3))) * u).astype(np.float32)
+_swiglu_of_interleaved = lambda full: O.gated_of_interleaved(full, "swiglu")
+_geglu_of_interleaved = lambda full: O.gated_of_interleaved(full, "geglu")
 
 
 @pytest.mark.parametrize("fmt", ["nvfp4", "fp8_block128", "bf16"])
