@@ -51,6 +51,9 @@ WORKLOADS = {
                                       act="swiglu", out="nvfp4"),
     "moe_fp8_groupwise_swiglu": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
                                      act="swiglu"),
+    # config C5 fed the way a layer feeds it: 16384 token rows + their routing; the tokens are quantised ONCE and the
+    # packed rows dispatched to expert-sorted order (step = plan + quantise + dispatch + grouped GEMM)
+    "moe_nvfp4_tokens": dict(kind="nvfp4", tokens_in=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
     # the whole MoE feed-forward layer around the two grouped GEMMs (router, plan, quantise once, dispatch,
     # gate/up GEMM with SwiGLU and NVFP4 result, down GEMM, combine); 0.01 = calibrated hidden global scale
     "moe_layer_nvfp4": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
@@ -124,6 +127,8 @@ def build_workload(name, rank, world, device, sets, strong=False):
     g = torch.Generator(device=device).manual_seed(1234 + rank)
     if cfg.get("layer"):
         return build_layer_workload(cfg, rank, world, device, sets, strong, g)
+    if cfg.get("tokens_in"):
+        return build_token_moe_workload(cfg, rank, device, sets)
     offs = None
     if cfg.get("moe"):
         experts = cfg["experts"]          # weak scaling keeps 64 local experts (and their routed rows) per GPU
@@ -198,10 +203,47 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
                 act="swiglu", out=None, layer=True, out_cols=D, out_rows=T // (world if strong else 1))
 
 
+def build_token_moe_workload(cfg, rank, device, sets):
+    """Grouped GEMM of an MoE layer from token-level input: x [tokens, K], ids [tokens, k] (seeded top-k routing)."""
+    from dsl_tool_b200 import moe, pack_weight, quantize_fp4
+    from dsl_tool_b200.gemm_kernels import gemm_fp4_quantized
+    T, E, k, K, N = cfg["tokens"], cfg["experts"], cfg["topk"], cfg["K"], cfg["N"]
+    acts, ids, wts = [], [], []
+    for s in range(sets):
+        gen = torch.Generator(device=device).manual_seed(55 + s + 1000 * rank)
+        acts.append(torch.randn((T, K), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16))
+        logits = torch.randn((T, E), generator=gen, device=device, dtype=torch.float32)
+        ids.append(torch.topk(logits, k, dim=1).indices.to(torch.int32).contiguous())
+        w = (torch.randn((E, N, K), generator=gen, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
+        wts.append(pack_weight(w, "nvfp4", layout="nk"))
+        del w
+    ones = torch.ones((T, k), dtype=torch.float32, device=device)
+    torch.cuda.synchronize()
+
+    def quant(i, a=None):
+        p = moe.plan(ids[i % sets], ones, E)
+        packed, sf, gs = quantize_fp4(acts[i % sets] if a is None else a, "nvfp4")
+        q, s = moe.dispatch_fp4(p, packed, sf, K, "nvfp4", 0, E)
+        return q, s, gs, p.offsets
+
+    def gemm(i, qs):
+        w = wts[i % sets]
+        return gemm_fp4_quantized(qs[0], w.q, qs[1], w.scale, format="nvfp4", n=N, global_scale_a=qs[2],
+                                  global_scale_b=w.global_scale, expert_offsets=qs[3], out_dtype=torch.bfloat16, b_static=True)
+
+    def step(i, a=None):
+        return gemm(i, quant(i, a))
+
+    return dict(step=step, acts=acts, wts=wts, offs=None, M=T * k, K=K, N=N, kind="nvfp4", flops=2.0 * T * k * N * K, moe=True,
+                act=None, out=None, split=(quant, gemm))
+
+
 def split_step(wl):
     """(quantise, gemm) closures so the GEMM launch can be bracketed by its own events."""
     if wl.get("layer"):
         return (lambda i: None), (lambda i, q: wl["step"](i))
+    if wl.get("split"):
+        return wl["split"]
     from dsl_tool_b200 import quantize_fp4, quantize_fp8
     from dsl_tool_b200 import gemm_kernels as GK
     kind, offs, sets = wl["kind"], wl["offs"], len(wl["acts"])
@@ -466,7 +508,7 @@ def main():
                 "ms_per_step": e2e_ms},
         # kernels of this library per step: quantiser passes + one GEMM kernel (NVFP4 tensors of up to
         # 2^18 elements are quantised by a single launch, larger ones by an amax pass + a quantise pass)
-        "gpu_launches": K_steps * 9 if wl.get("layer") else K_steps * ({"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
+        "gpu_launches": K_steps * 9 if wl.get("layer") else K_steps * 7 if wl.get("split") else K_steps * ({"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
                                     "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]),
         "cuda_graph": bool(args.graph),
         "clocks": clocks,
