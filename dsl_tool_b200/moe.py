@@ -23,7 +23,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from .gemm_kernels import gemm_fp4_quantized, gemm_fp8_quantized, linear
+from .gemm_kernels import gemm_fp4_quantized, gemm_fp8_groupwise_quantized, gemm_fp8_quantized, linear
 from .quantize import PackedWeight, pack_weight, quantize_fp4, quantize_fp8
 from .sharding import expert_ranges
 
@@ -70,6 +70,12 @@ def plan(ids: torch.Tensor, weights: torch.Tensor, experts: int) -> MoEPlan:
                                      dest.data_ptr(), _lib.stream_ptr())
     _lib.check(rc, "dsl_moe_plan")
     return MoEPlan(ids, weights.contiguous(), offsets, tile0, dest, experts)
+
+
+def _pad_cols(t: torch.Tensor, multiple: int) -> torch.Tensor:
+    """Pads the last dimension with zeros to a multiple (rows of fp32 scales must be multiples of 16 bytes to be dispatched)."""
+    extra = -t.shape[1] % multiple
+    return t if extra == 0 else torch.nn.functional.pad(t, (0, extra))
 
 
 def _local_offsets(p: MoEPlan, first: int, last: int) -> torch.Tensor:
@@ -190,6 +196,14 @@ def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
         qh, sh = quantize_fp8(h[:n_local], "per_tensor")
         y = gemm_fp8_quantized(qh, w.down.q, sh, w.down.scale, n=w.down.n, expert_offsets=offs, out_dtype=torch.bfloat16,
                                b_static=True)
+    elif fmt == "fp8_block128":
+        # 1x128 activation groups: quantised once per token; the E4M3 rows and their scale rows are dispatched
+        qa, sa = quantize_fp8(x, "groupwise")
+        rows = dispatch_rows(p, qa, w.first, w.last)
+        sa_rows = dispatch_rows(p, _pad_cols(sa, 4), w.first, w.last)[:, :sa.shape[1]].contiguous()
+        h = gemm_fp8_groupwise_quantized(rows, w.gate_up.q, sa_rows, w.gate_up.scale, n=w.gate_up.n, sb_block=True,
+                                         expert_offsets=offs, activation="swiglu", out_dtype=torch.bfloat16)
+        y = linear(h, w.down, expert_offsets=offs, out_dtype=torch.bfloat16)     # rows are independent: unwritten ones harm nobody
     else:
         rows = dispatch_rows(p, x.to(torch.bfloat16), w.first, w.last)
         h = linear(rows, w.gate_up, expert_offsets=offs, activation="swiglu", out_dtype=torch.bfloat16)

@@ -148,7 +148,7 @@ def test_layer_equals_its_unfused_composition(cuda_device):
     assert rel < 0.25
 
 
-@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "bf16", "fp8"])
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4", "bf16", "fp8", "fp8_block128"])
 def test_expert_parallel_partials_add_up(cuda_device, fmt):
     """Two ranks' shares of the experts, computed on this one GPU, sum to the single-rank result."""
     rng = np.random.default_rng(41)
