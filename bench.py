@@ -64,6 +64,7 @@ DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1"
 # dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from an ncu capture of the
 # full-size workload (profiles/): bytes.  None where no capture exists.
 NCU_TRAFFIC = {"fp8_groupwise_llama8b_mlp": 77.1e6 + 74.9e6,
+               "nvfp4_8192": 164.5e6 + 105.9e6,
                "nvfp4_m16": 37.93e6 + 0.28e6}      # decode: GEMM + quantiser launch (whole step)
 PEAK_MULT = {"fp8": 2.0, "fp8_block128": 2.0, "nvfp4": 4.0, "mxfp4": 4.0, "bf16": 1.0}
 
