@@ -335,16 +335,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int cb = rot ? ((j + 7) & 7) : j + 1;
                 tmem_ld_wait();
                 tmem_ld_32x32b_x32(t_row + cb * 32, vb);
+                if (C::SF_ATOMS > 0 && j == 0) {
+                    // chunks 0 and 1 of this walk are the columns shared with the other accumulator: hand them back as
+                    // soon as both are in registers, before any of the slower scale / convert / store work
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(ovl_free, 0);
+                }
                 if (warp_store && ti.n0 + ca * 32 + 32 <= args.n)
                     store_chunk32_bf16_warp(args, epi_scratch, row_warp, ti.row_end, ti.n0 + ca * 32, ti.group, va, s1, s2, rs, lane);
                 else if (row_ok && ti.n0 + ca * 32 < args.n)
                     store_chunk32(args, row, ti.n0 + ca * 32, ti.group, va, s1, s2, rs, vec_ok, ti.sf_tile + static_cast<int>(rank), quad * 32 + lane);
                 tmem_ld_wait();
-                if (C::SF_ATOMS > 0 && j == 0) {       // chunks 0 and 1 of this walk (the shared columns) are in registers
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(ovl_free, 0);
-                }
                 if (j + 2 < pr::TILE_N / 32) tmem_ld_32x32b_x32(t_row + (rot ? ((j + 8) & 7) : j + 2) * 32, va);
                 if (warp_store && ti.n0 + cb * 32 + 32 <= args.n)
                     store_chunk32_bf16_warp(args, epi_scratch, row_warp, ti.row_end, ti.n0 + cb * 32, ti.group, vb, s1, s2, rs, lane);
