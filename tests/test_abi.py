@@ -72,3 +72,55 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libdslgemm.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.lib()
+
+
+def test_epilogue_struct_layout_matches_the_header(tmp_path):
+    """The ctypes mirror of dsl_epilogue has the size and field offsets the C compiler gives the header's struct."""
+    import subprocess
+    fields = [name for name, _ in _lib.Epilogue._fields_]
+    src = tmp_path / "layout.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "dslgemm.h"', 'int main(void) {',
+             '  printf("%zu\\n", sizeof(dsl_epilogue));']
+    lines += [f'  printf("{f} %zu\\n", offsetof(dsl_epilogue, {f}));' for f in fields]
+    lines += ['  return 0;', '}']
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    assert int(out[0]) == ctypes.sizeof(_lib.Epilogue)
+    for line in out[1:]:
+        if line:
+            name, off = line.split()
+            assert getattr(_lib.Epilogue, name).offset == int(off), name
+    # and the header's enum values are the ones the binding uses
+    text = open(os.path.join(ROOT, "include", "dslgemm.h")).read()
+    for cname, value in (("DSL_ACT_SWIGLU", _lib.ACT_SWIGLU), ("DSL_ACT_GEGLU", _lib.ACT_GEGLU), ("DSL_OUT_NVFP4", _lib.OUT_NVFP4)):
+        assert re.search(rf"\b{cname}\s*=\s*{value}\b", text), cname
+
+
+def test_new_argument_validation_without_gpu(cdll):
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf) & ~15
+    ep = _lib.Epilogue()
+    ep.activation = 7
+    assert cdll.dsl_gemm_fp8(p, p, p, 16, 4, 16, 32, None, 1, ctypes.byref(ep), None, None) == -4      # unknown activation
+    ep.activation = _lib.ACT_SWIGLU
+    assert cdll.dsl_gemm_fp8(p, p, p, 16, 4, 15, 32, None, 1, ctypes.byref(ep), None, None) == -2      # odd column count
+    assert cdll.dsl_gemm_fp8(p, p, p, 4, 4, 16, 32, None, 1, ctypes.byref(ep), None, None) == -2       # ldc < N/2
+    ep.activation = 0
+    ep.out_dtype = _lib.OUT_NVFP4
+    assert cdll.dsl_gemm_fp8(p, p, p, 32, 4, 32, 32, None, 1, ctypes.byref(ep), None, None) == -1      # no out_sf
+    ep.out_sf = p
+    assert cdll.dsl_gemm_fp8(p, p, p, 32, 4, 32, 32, None, 1, ctypes.byref(ep), None, None) == -2      # no global scale
+    ep.out_gs_host = 0.01
+    assert cdll.dsl_gemm_fp8(p, p, p, 24, 4, 24, 32, None, 1, ctypes.byref(ep), None, None) == -2      # columns % 16
+    assert cdll.dsl_gemm_fp8_groupwise(p, p, p, p, 1, p, 32, 4, 32, 128, None, 1, ctypes.byref(ep), None, None) == -4
+    assert cdll.dsl_moe_route(p, 0, 4, 8, 9, 1, p, p, None) == -2                                      # k > experts
+    assert cdll.dsl_moe_route(p, 2, 4, 8, 2, 1, p, p, None) == -4                                      # fp16 logits
+    assert cdll.dsl_moe_plan(p, 8, 5000, p, p, p, p, None) == -2
+    assert cdll.dsl_moe_plan_scratch_bytes(4096, 64) == (2 + 1) * 64 * 4
+    assert cdll.dsl_moe_dispatch_fp4(p, p, p, p, p, p, 4, 2, 48, 0, 0, 4, p, p, None) == -2            # K % 32
+    assert cdll.dsl_moe_dispatch_rows(p, p, p, p, 4, 2, 24, 0, 4, p, None) == -2                       # row bytes % 16
+    assert cdll.dsl_moe_combine(p, 0, p, p, p, p, 4, 40, 16, 0, 4, p, 0, None) == -2                   # k > 32
+    assert cdll.dsl_quant_fp4_ref32(None, 0, 64, p, p, None) == -1
+    assert cdll.dsl_gemm_fp4_ref32(p, p, p, p, p, 4, 8, 48, None) == -2                                # K % 32
