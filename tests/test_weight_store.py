@@ -141,3 +141,13 @@ def test_packed_file_spec(tmp_path):
     got = deserialize_tensor({"packed_file": str(p)}, device="cpu")
     assert isinstance(got, PackedWeight)
     _same(got, w)
+
+
+def test_host_pipeline_chunk_bounds_and_no_cpu_path():
+    from dsl_tool_b200.host_io import HostPipeline, chunk_bounds
+    assert chunk_bounds(10, 4) == [(0, 4), (4, 8), (8, 10)] and chunk_bounds(0, 4) == [] and chunk_bounds(4, 4) == [(0, 4)]
+    with pytest.raises(ValueError):
+        chunk_bounds(4, 0)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            HostPipeline(lambda a: a, "cuda:0")
