@@ -33,6 +33,7 @@ struct GemmArgs {
     long long ldc;
     int out_bf16;
     int band;                    // column tiles per raster band (L2 reuse)
+    int whole_tiles_only;        // 1: the tiles after the last full round are not cut into narrow pieces (measurements)
     int split_k;                 // > 1: K is cut into this many slices whose fp32 partial sums go to `partial`
     float* partial;              // [split_k, m_total, n] scratch (dense problems only)
     size_t partial_bytes;        // capacity of `partial`

@@ -39,19 +39,40 @@ constexpr int SMEM_BYTES = OFF_TABLE + 2 * (DSL_MAX_GROUPS + 1) * 4 + 1024;
 constexpr int THREADS = 320;
 static_assert(SMEM_BYTES > 116224 && SMEM_BYTES <= 232448, "one CTA per SM");
 
+constexpr int NARROW_N = 64;                 // width of the pieces a last-round tile is cut into
+constexpr int NARROW_PARTS = TILE_N / NARROW_N;
+constexpr int B_NARROW = (NARROW_N / 2) * STAGE_KB;   // bytes of B each CTA loads per stage for a narrow piece
+
 struct Tile {
-    int group, row0, row_end, n0;
+    int group, row0, row_end, n0, width;
 };
 
 struct Walker {
     const int* offs;
     const int* tile0;
     int groups, m_tiles, n_tiles, band;
-    long long total;
-    __device__ __forceinline__ Tile decode(long long t) const {
-        const long long per_band = static_cast<long long>(m_tiles) * band;
-        const int b = static_cast<int>(t / per_band);
-        const int r = static_cast<int>(t - b * per_band);
+    int total;         // 256 x 256 tiles (the launcher refuses shapes with more than 2^29 of them)
+    int full;          // tiles [0, full) run at full width; each tile of [full, total) as NARROW_PARTS pieces
+    int items;         // work items of the whole launch
+    // The tiles left over after the last full round of the grid would keep a few CTA pairs busy for a whole
+    // tile time while the others idle; when all their 64-column pieces fit into one round they are cut up.
+    // Every output element still sums the same K groups in the same order, so the result does not change.
+    __device__ __forceinline__ void plan(int pairs) {
+        const int rest = total % pairs;
+        full = (total > pairs && rest > 0 && rest * NARROW_PARTS <= pairs) ? total - rest : total;
+        items = full + (total - full) * NARROW_PARTS;
+    }
+    __device__ __forceinline__ Tile decode(int item) const {
+        int t = item, part = 0, width = TILE_N;
+        if (item >= full) {
+            const int q = item - full;
+            t = full + q / NARROW_PARTS;
+            part = q % NARROW_PARTS;
+            width = NARROW_N;
+        }
+        const int per_band = m_tiles * band;
+        const int b = t / per_band;
+        const int r = t - b * per_band;
         const int nb0 = b * band;
         const int wb = min(band, n_tiles - nb0);
         const int mt = r / wb;
@@ -65,17 +86,97 @@ struct Walker {
         ti.group = lo;
         ti.row0 = offs[lo] + (mt - tile0[lo]) * TILE_M;
         ti.row_end = offs[lo + 1];
-        ti.n0 = nt * TILE_N;
+        ti.n0 = nt * TILE_N + part * NARROW_N;
+        ti.width = width;
         return ti;
     }
 };
 
 }  // namespace gwp
 
+// One tile of the promotion warps' work: PIECES 16-column pieces of this warp's half of the tile, K group by K group.
+template <bool SB_BLOCK, bool ACT, int PIECES>   // a warp's share is PIECES * 16 adjacent columns; half 1 starts right after half 0's
+__device__ __forceinline__ bool promote_tile(const GemmArgs& args, const gwp::Tile& ti, int num_kb, int nb128, uint32_t tmem_base,
+                                             uint64_t* part_full, uint64_t* part_empty, volatile uint32_t* abort_flag,
+                                             uint32_t& step, int rank, int quad, int half, int lane) {
+    using namespace gwp;
+    const int row = ti.row0 + 128 * rank + quad * 32 + lane;
+    const bool row_ok = row < ti.row_end;
+    const int col_base = ti.n0 + half * (PIECES * 16);
+    const float* sa_row = args.gsa + static_cast<size_t>(row_ok ? row : ti.row0) * num_kb;
+    const float* sb_ptr;
+    if (SB_BLOCK) {
+        const int nb = min(col_base / 128, nb128 - 1);
+        sb_ptr = args.gsb + (static_cast<size_t>(ti.group) * nb128 + nb) * num_kb;
+    } else {
+        sb_ptr = args.gsb + static_cast<size_t>(ti.group) * num_kb * args.n;
+    }
+    float acc[PIECES * 16];
+#pragma unroll
+    for (int i = 0; i < PIECES * 16; ++i) acc[i] = 0.f;
+    float sa_next = __ldg(sa_row);
+    float sb_next = SB_BLOCK ? __ldg(sb_ptr) : 0.f;
+    for (int kb = 0; kb < num_kb; ++kb, ++step) {
+        const float sa = sa_next;
+        const float s = SB_BLOCK ? __fmul_rn(sa, sb_next) : 0.f;
+        if (kb + 1 < num_kb) {   // next group's scales are fetched while this one is promoted
+            sa_next = __ldg(sa_row + kb + 1);
+            if (SB_BLOCK) sb_next = __ldg(sb_ptr + kb + 1);
+        }
+        const int p = static_cast<int>(step & 1);
+        const uint32_t pphase = (step >> 1) & 1u;
+        if (!mbar_wait_cluster(part_full + p, pphase, abort_flag, ST_TIMEOUT_EPILOGUE)) return false;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + p * TILE_N + half * (PIECES * 16) + (static_cast<uint32_t>(quad * 32) << 16);
+        uint32_t buf[2][16];
+        tmem_ld_32x32b_x16(taddr, buf[0]);
+#pragma unroll
+        for (int c = 0; c < PIECES; ++c) {
+            tmem_ld_wait();
+            if (c + 1 < PIECES) {
+                tmem_ld_32x32b_x16(taddr + (c + 1) * 16, buf[(c + 1) & 1]);
+            } else {   // the whole partial product is in registers: hand the buffer back now
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(part_empty + p, 0);
+            }
+            if (SB_BLOCK) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    acc[c * 16 + i] = fmaf(__uint_as_float(buf[c & 1][i]), s, acc[c * 16 + i]);
+            } else {
+                const float* sbrow = sb_ptr + static_cast<size_t>(kb) * args.n;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int col = col_base + c * 16 + i;
+                    const float sb = col < args.n ? __ldg(sbrow + col) : 0.f;
+                    acc[c * 16 + i] = fmaf(__fmul_rn(__uint_as_float(buf[c & 1][i]), sa), sb, acc[c * 16 + i]);
+                }
+            }
+        }
+    }
+    if (!row_ok) return true;
+    // read here, once per tile, so that they hold no registers during the promotion
+    const float s1 = args.s1_dev != nullptr ? *args.s1_dev : args.s1;
+    const float s2 = args.s2_dev != nullptr ? *args.s2_dev : args.s2;
+    const bool vec_ok = args.out_bf16 ? (args.ldc % 8 == 0) : (args.ldc % 4 == 0);
+    const float rs = args.row_scale != nullptr ? args.row_scale[row] : 1.0f;
+#pragma unroll
+    for (int c = 0; c < PIECES / 2; ++c) {
+        const int col0 = col_base + c * 32;
+        if (col0 >= args.n) continue;
+        uint32_t v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(acc[c * 32 + i]);
+        store_chunk32_t<ACT>(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
+    }
+    return true;
+}
+
 template <bool SB_BLOCK, bool ACT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gwp::THREADS, 1)
 gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                               const GemmArgs args) {
+                               const __grid_constant__ CUtensorMap tmap_b_narrow, const GemmArgs args) {
     using namespace gwp;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -93,8 +194,8 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
-    const long long pair_id = blockIdx.x >> 1;
-    const long long num_pairs = gridDim.x >> 1;
+    const int pair_id = static_cast<int>(blockIdx.x >> 1);
+    const int num_pairs = static_cast<int>(gridDim.x >> 1);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < NUM_STAGES; ++i) {
@@ -107,6 +208,7 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        prefetch_tmap(&tmap_b_narrow);
     }
     for (int g = threadIdx.x; g <= groups; g += blockDim.x)
         s_offs[g] = args.group_offsets != nullptr ? args.group_offsets[g] : (g == 0 ? 0 : args.m_total);
@@ -136,23 +238,30 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     tw.m_tiles = s_tile0[groups];
     tw.n_tiles = (args.n + TILE_N - 1) / TILE_N;
     tw.band = args.band < 1 ? 1 : args.band;
-    tw.total = static_cast<long long>(tw.m_tiles) * tw.n_tiles;
+    tw.total = tw.m_tiles * tw.n_tiles;
+    tw.plan(num_pairs);
+    if (args.whole_tiles_only) { tw.full = tw.total; tw.items = tw.total; }
     const int num_kb = args.k_bytes / STAGE_KB;   // K % 128 == 0
 
     if (warp == 0) {
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+        for (int t = pair_id; t < tw.items && ok; t += num_pairs) {
             const Tile ti = tw.decode(t);
+            const bool narrow = ti.width != TILE_N;
             for (int kb = 0; kb < num_kb; ++kb) {
                 if (!mbar_wait_cluster(empty_bar + stage, phase ^ 1u, abort_flag, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                 if (elect_one()) {
-                    mbar_arrive_expect_tx(full_bar + stage, A_STAGE + B_STAGE);
+                    mbar_arrive_expect_tx(full_bar + stage, A_STAGE + (narrow ? B_NARROW : B_STAGE));
                     tma_load_2d(smem + OFF_A + stage * A_STAGE, &tmap_a, full_bar + stage, kb * STAGE_KB,
                                 ti.row0 + 128 * static_cast<int>(rank));
-                    tma_load_3d(smem + OFF_B + stage * B_STAGE, &tmap_b, full_bar + stage, kb * STAGE_KB,
-                                ti.n0 + 128 * static_cast<int>(rank), ti.group);
+                    if (narrow)
+                        tma_load_3d(smem + OFF_B + stage * B_STAGE, &tmap_b_narrow, full_bar + stage, kb * STAGE_KB,
+                                    ti.n0 + (NARROW_N / 2) * static_cast<int>(rank), ti.group);
+                    else
+                        tma_load_3d(smem + OFF_B + stage * B_STAGE, &tmap_b, full_bar + stage, kb * STAGE_KB,
+                                    ti.n0 + 128 * static_cast<int>(rank), ti.group);
                 }
                 __syncwarp();
                 if (++stage == NUM_STAGES) { stage = 0; phase ^= 1u; }
@@ -160,16 +269,19 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         }
     } else if (warp == 1) {
         if (rank == 0) {
-            const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(TILE_N >> 3) << 17) |
-                                   (static_cast<uint32_t>(TILE_M >> 4) << 24);   // E4M3 x E4M3 -> fp32
+            const uint32_t idesc_full = (1u << 4) | (static_cast<uint32_t>(TILE_N >> 3) << 17) |
+                                        (static_cast<uint32_t>(TILE_M >> 4) << 24);   // E4M3 x E4M3 -> fp32
+            const uint32_t idesc_narrow = (1u << 4) | (static_cast<uint32_t>(NARROW_N >> 3) << 17) |
+                                          (static_cast<uint32_t>(TILE_M >> 4) << 24);
             int stage = 0;
             uint32_t phase = 0;
-            long long step = 0;
+            uint32_t step = 0;   // only its two low bits matter (buffer and phase)
             bool ok = true;
-            for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+            for (int t = pair_id; t < tw.items && ok; t += num_pairs) {
+                const uint32_t idesc = t >= tw.full ? idesc_narrow : idesc_full;
                 for (int kb = 0; kb < num_kb; ++kb, ++step) {
                     const int p = static_cast<int>(step & 1);
-                    const uint32_t pphase = static_cast<uint32_t>((step >> 1) & 1);
+                    const uint32_t pphase = (step >> 1) & 1u;
                     if (!mbar_wait_cluster(part_empty + p, pphase ^ 1u, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     if (!mbar_wait_cluster(peer_full + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
@@ -191,7 +303,7 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+            for (int t = pair_id; t < tw.items && ok; t += num_pairs) {
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     if (lane == 0) mbar_arrive_cluster(peer_full + stage, 0);
@@ -204,81 +316,18 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         // ================= promotion + epilogue =================
         const int quad = warp & 3;
         const int half = (warp - 2) >> 2;
-        const float s1 = args.s1_dev != nullptr ? *args.s1_dev : args.s1;
-        const float s2 = args.s2_dev != nullptr ? *args.s2_dev : args.s2;
-        const bool vec_ok = args.out_bf16 ? (args.ldc % 8 == 0) : (args.ldc % 4 == 0);
         const int nb128 = (args.n + 127) / 128;
-        long long step = 0;
+        uint32_t step = 0;
         bool ok = true;
-        for (long long t = pair_id; t < tw.total && ok; t += num_pairs) {
+        for (int t = pair_id; t < tw.items && ok; t += num_pairs) {
             const Tile ti = tw.decode(t);
-            const int row = ti.row0 + 128 * static_cast<int>(rank) + quad * 32 + lane;
-            const bool row_ok = row < ti.row_end;
-            const int col_base = ti.n0 + half * 128;
-            const float* sa_row = args.gsa + static_cast<size_t>(row_ok ? row : ti.row0) * num_kb;
-            const float* sb_ptr;
-            if (SB_BLOCK) {
-                const int nb = min(col_base / 128, nb128 - 1);
-                sb_ptr = args.gsb + (static_cast<size_t>(ti.group) * nb128 + nb) * num_kb;
-            } else {
-                sb_ptr = args.gsb + static_cast<size_t>(ti.group) * num_kb * args.n;
-            }
-            float acc[128];
-#pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-            float sa_next = __ldg(sa_row);
-            float sb_next = SB_BLOCK ? __ldg(sb_ptr) : 0.f;
-            for (int kb = 0; kb < num_kb; ++kb, ++step) {
-                const float sa = sa_next;
-                const float s = SB_BLOCK ? __fmul_rn(sa, sb_next) : 0.f;
-                if (kb + 1 < num_kb) {   // next group's scales are fetched while this one is promoted
-                    sa_next = __ldg(sa_row + kb + 1);
-                    if (SB_BLOCK) sb_next = __ldg(sb_ptr + kb + 1);
-                }
-                const int p = static_cast<int>(step & 1);
-                const uint32_t pphase = static_cast<uint32_t>((step >> 1) & 1);
-                if (!mbar_wait_cluster(part_full + p, pphase, abort_flag, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t taddr = tmem_base + p * TILE_N + half * 128 + (static_cast<uint32_t>(quad * 32) << 16);
-                uint32_t buf[2][16];
-                tmem_ld_32x32b_x16(taddr, buf[0]);
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    tmem_ld_wait();
-                    if (c + 1 < 8) {
-                        tmem_ld_32x32b_x16(taddr + (c + 1) * 16, buf[(c + 1) & 1]);
-                    } else {   // the whole partial product is in registers: hand the buffer back now
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(part_empty + p, 0);
-                    }
-                    if (SB_BLOCK) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            acc[c * 16 + i] = fmaf(__uint_as_float(buf[c & 1][i]), s, acc[c * 16 + i]);
-                    } else {
-                        const float* sbrow = sb_ptr + static_cast<size_t>(kb) * args.n;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int col = col_base + c * 16 + i;
-                            const float sb = col < args.n ? __ldg(sbrow + col) : 0.f;
-                            acc[c * 16 + i] = fmaf(__fmul_rn(__uint_as_float(buf[c & 1][i]), sa), sb, acc[c * 16 + i]);
-                        }
-                    }
-                }
-            }
-            if (!ok) break;
-            if (!row_ok) continue;
-            const float rs = args.row_scale != nullptr ? args.row_scale[row] : 1.0f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int col0 = col_base + c * 32;
-                if (col0 >= args.n) continue;
-                uint32_t v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(acc[c * 32 + i]);
-                store_chunk32_t<ACT>(args, row, col0, ti.group, v, s1, s2, rs, vec_ok);
-            }
+            // full width: 128 columns per warp; a 64-column piece: 32 per warp
+            if (ti.width == TILE_N)
+                ok = promote_tile<SB_BLOCK, ACT, TILE_N / 32>(args, ti, num_kb, nb128, tmem_base, part_full, part_empty, abort_flag, step,
+                                                              static_cast<int>(rank), quad, half, lane);
+            else
+                ok = promote_tile<SB_BLOCK, ACT, NARROW_N / 32>(args, ti, num_kb, nb128, tmem_base, part_full, part_empty, abort_flag,
+                                                                step, static_cast<int>(rank), quad, half, lane);
         }
     }
 
@@ -300,10 +349,11 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
 
 template <bool SB_BLOCK, bool ACT>
 static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tbn;
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
     if (!make_tmap_u8(&ta, A, args.k_bytes, args.m_total, 0, STAGE_KB, 128)) return DSL_ERR_DRIVER;
     if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, 128)) return DSL_ERR_DRIVER;
+    if (!make_tmap_u8(&tbn, B, args.k_bytes, args.n, groups, STAGE_KB, gwp::NARROW_N / 2)) return DSL_ERR_DRIVER;
     static int max_clusters = 0;
     if (max_clusters == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>,
@@ -323,15 +373,20 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     }
     const long long m_tiles_max = (args.m_total + gwp::TILE_M - 1) / gwp::TILE_M + groups - 1;
     const long long max_tiles = m_tiles_max * ((args.n + gwp::TILE_N - 1) / gwp::TILE_N);
+    if (max_tiles > (1ll << 29)) return DSL_ERR_SHAPE;   // tile counters in the kernel are 32-bit
     long long clusters = max_tiles < max_clusters ? max_tiles : max_clusters;
     if (clusters < 1) clusters = 1;
-    gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT><<<static_cast<unsigned>(2 * clusters), gwp::THREADS, gwp::SMEM_BYTES, st>>>(ta, tb, args);
+    gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT><<<static_cast<unsigned>(2 * clusters), gwp::THREADS, gwp::SMEM_BYTES, st>>>(ta, tb, tbn, args);
     return static_cast<int>(cudaGetLastError());
 }
 
 int launch_gemm_fp8_groupwise_pair(const void* A, const void* B, GemmArgs args, cudaStream_t st) {
     if (args.m_total <= 0 || args.n <= 0) return 0;
     if (args.band <= 0) args.band = 8;
+    {   // DSLGEMM_WHOLE_TILES=1 keeps every tile whole (for measurements)
+        static const int whole = [] { const char* e = getenv("DSLGEMM_WHOLE_TILES"); return (e != nullptr && e[0] == '1') ? 1 : 0; }();
+        args.whole_tiles_only = whole;
+    }
     // two instantiations: the plain epilogue keeps the promotion loop free of spills, the activation one is larger
     if (args.act != DSL_ACT_NONE)
         return args.sb_block ? launch_gw_pair<true, true>(A, B, args, st) : launch_gw_pair<false, true>(A, B, args, st);

@@ -79,27 +79,40 @@ __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
     float s = __fdiv_rn(amax, 448.0f);
     return s < 1e-12f ? 1e-12f : s;
 }
-// x / s for the E4M3 conversion, bit-identical in effect to the IEEE quotient but cheaper: the
-// product x * rcp(s) is within 2 ulp of the correctly rounded quotient, so both round to the
-// same E4M3 code unless the product lies within 2 ulp of a rounding boundary of the 3-bit
-// mantissa (low 20 bits = 0x80000) or in the subnormal range of E4M3 (|r| < 2^-6, where the
-// boundaries sit elsewhere); only those rare elements take the true division.
+// x / s for the E4M3 conversion without a division per element.  With y = RN(1/s) shared by the
+// 16 elements, q0 = RN(x*y) is within 2 ulp of the quotient; one residual correction
+// (r = x - q*s exactly, by FMA; q' = RN(q + r*y)) brings it within half an ulp plus a sliver, and a
+// second one gives the correctly rounded quotient (Markstein's theorem: a faithful q and a correctly
+// rounded reciprocal suffice), i.e. the very value __fdiv_rn returns.  The residual is exact unless
+// it underflows, which needs |x| < 2^-125; the scale is at least 1e-12, so such a quotient is below
+// 2^-85, far under the smallest E4M3 rounding boundary (2^-10), and converts to zero either way.
+// Two values of q0 must pass through untouched: a zero (the zero residual is +0 and would turn -0
+// into +0) and an infinity (Inf - Inf poisons the residual); both are the fixed points of q -> 2q.
+// A NaN stays a NaN through the corrections.  Six FMA-pipe instructions, one compare and one select
+// per element instead of a reciprocal and range checks.
 __device__ __forceinline__ float div_for_e4m3(float x, float s, float inv) {
-    float r = __fmul_rn(x, inv);
-    const uint32_t b = __float_as_uint(r);
-    const bool near_tie = ((b & 0xFFFFFu) - 0x7FFFEu) <= 4u;
-    const bool small = (b & 0x7FFFFFFFu) < 0x3C800000u;   // |r| < 2^-6, zero included
-    if (near_tie || small) r = __fdiv_rn(x, s);
-    return r;
+    const float q0 = __fmul_rn(x, inv);
+    const float q1 = __fmaf_rn(__fmaf_rn(-q0, s, x), inv, q0);
+    const float q2 = __fmaf_rn(__fmaf_rn(-q1, s, x), inv, q1);
+    return __fadd_rn(q0, q0) == q0 ? q0 : q2;
 }
 __device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
-    const float inv = __frcp_rn(s);
     uint32_t w[4];
+    if (s <= 3.0e38f) {
+        const float inv = __frcp_rn(s);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint32_t lo = cvt_e4m3x2(div_for_e4m3(v[4 * i], s, inv), div_for_e4m3(v[4 * i + 1], s, inv));
-        uint32_t hi = cvt_e4m3x2(div_for_e4m3(v[4 * i + 2], s, inv), div_for_e4m3(v[4 * i + 3], s, inv));
-        w[i] = lo | (hi << 16);
+        for (int i = 0; i < 4; ++i) {
+            uint32_t lo = cvt_e4m3x2(div_for_e4m3(v[4 * i], s, inv), div_for_e4m3(v[4 * i + 1], s, inv));
+            uint32_t hi = cvt_e4m3x2(div_for_e4m3(v[4 * i + 2], s, inv), div_for_e4m3(v[4 * i + 3], s, inv));
+            w[i] = lo | (hi << 16);
+        }
+    } else {   // an infinite scale (an Inf among the inputs): 0 * Inf would poison the residual; divide for real
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t lo = cvt_e4m3x2(__fdiv_rn(v[4 * i], s), __fdiv_rn(v[4 * i + 1], s));
+            uint32_t hi = cvt_e4m3x2(__fdiv_rn(v[4 * i + 2], s), __fdiv_rn(v[4 * i + 3], s));
+            w[i] = lo | (hi << 16);
+        }
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
 }

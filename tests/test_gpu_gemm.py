@@ -85,6 +85,29 @@ def test_fp8_groupwise(cuda_device, sb_block, M, N, K):
     assert rel_frobenius(got.cpu().numpy(), want) <= REL_FROB_TOL
 
 
+@pytest.mark.parametrize("sb_block", [True, False])
+@pytest.mark.parametrize("M,N", [(2560, 2000), (2304, 2304)])
+def test_fp8_groupwise_last_round_cut_into_pieces(cuda_device, sb_block, M, N):
+    """80 / 81 tiles of 256 x 256 on 74 CTA pairs: the tiles after the last full round run as 64-column pieces
+    (also past a ragged right edge).  The pieces sum the same K groups in the same order, so besides matching the
+    oracle the first 256 rows must equal, bit for bit, the same rows multiplied alone (8 / 9 tiles, nothing cut)."""
+    from dsl_tool_b200.gemm_kernels import gemm_fp8_groupwise_quantized
+    K = 384
+    rng = np.random.default_rng(M + N)
+    qa, sa = O.quant_fp8_groupwise(activations(rng, M, K))
+    qb, sbb = O.quant_fp8_block(weights(rng, N, K))
+    sb_col = O.expand_block_scale(sbb, N)
+    want = O.gemm_fp8_groupwise(qa, qb, sa, sb_col)
+    sb = _t(sbb[None]) if sb_block else _t(sb_col[None])
+    got = gemm_fp8_groupwise_quantized(_t(qa), _t(qb), _t(sa), sb, n=N, sb_block=sb_block)
+    _status_ok()
+    assert rel_frobenius(got.cpu().numpy(), want) <= REL_FROB_TOL
+    for r0 in (0, M - 256):
+        alone = gemm_fp8_groupwise_quantized(_t(qa[r0:r0 + 256]), _t(qb), _t(sa[r0:r0 + 256]), sb, n=N, sb_block=sb_block)
+        _status_ok()
+        assert torch.equal(got[r0:r0 + 256], alone)
+
+
 def test_epilogue_row_and_column_rescale(cuda_device):
     from dsl_tool_b200.gemm_kernels import gemm_fp8_quantized
     rng = np.random.default_rng(5)
