@@ -32,7 +32,8 @@ constexpr int NUM_STAGES = 6;
 constexpr int OFF_A = 0;
 constexpr int OFF_B = NUM_STAGES * A_STAGE;
 constexpr int OFF_BAR = OFF_B + NUM_STAGES * B_STAGE;
-constexpr int NUM_BARS = 3 * NUM_STAGES + 4;
+constexpr int NARROW_RING = 4;                // accumulator buffers of a narrow piece (64 columns each)
+constexpr int NUM_BARS = 3 * NUM_STAGES + 4 + 2 * NARROW_RING;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
 constexpr int OFF_TABLE = OFF_MISC + 16;
 constexpr int SMEM_BYTES = OFF_TABLE + 2 * (DSL_MAX_GROUPS + 1) * 4 + 1024;
@@ -95,7 +96,9 @@ struct Walker {
 }  // namespace gwp
 
 // One tile of the promotion warps' work: PIECES 16-column pieces of this warp's half of the tile, K group by K group.
-template <bool SB_BLOCK, bool ACT, int PIECES>   // a warp's share is PIECES * 16 adjacent columns; half 1 starts right after half 0's
+// A warp's share is PIECES * 16 adjacent columns, half 1 starting right after half 0's.  The partial products arrive in a
+// ring of RING tensor-memory buffers PIECES * 32 columns apart; `step` counts the K groups this ring has carried.
+template <bool SB_BLOCK, bool ACT, int PIECES, int RING>
 __device__ __forceinline__ bool promote_tile(const GemmArgs& args, const gwp::Tile& ti, int num_kb, int nb128, uint32_t tmem_base,
                                              uint64_t* part_full, uint64_t* part_empty, volatile uint32_t* abort_flag,
                                              uint32_t& step, int rank, int quad, int half, int lane) {
@@ -123,11 +126,11 @@ __device__ __forceinline__ bool promote_tile(const GemmArgs& args, const gwp::Ti
             sa_next = __ldg(sa_row + kb + 1);
             if (SB_BLOCK) sb_next = __ldg(sb_ptr + kb + 1);
         }
-        const int p = static_cast<int>(step & 1);
-        const uint32_t pphase = (step >> 1) & 1u;
+        const int p = static_cast<int>(step % RING);
+        const uint32_t pphase = (step / RING) & 1u;
         if (!mbar_wait_cluster(part_full + p, pphase, abort_flag, ST_TIMEOUT_EPILOGUE)) return false;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + p * TILE_N + half * (PIECES * 16) + (static_cast<uint32_t>(quad * 32) << 16);
+        const uint32_t taddr = tmem_base + p * (PIECES * 32) + half * (PIECES * 16) + (static_cast<uint32_t>(quad * 32) << 16);
         uint32_t buf[2][16];
         tmem_ld_32x32b_x16(taddr, buf[0]);
 #pragma unroll
@@ -185,6 +188,8 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     uint64_t* empty_bar = peer_full + NUM_STAGES;
     uint64_t* part_full = empty_bar + NUM_STAGES;     // [2] partial product complete (both CTAs)
     uint64_t* part_empty = part_full + 2;             // [2] leader only: all 16 promotion warps drained the buffer
+    uint64_t* nar_full = part_empty + 2;              // [NARROW_RING] the same pair of rings for a narrow piece
+    uint64_t* nar_empty = nar_full + NARROW_RING;     // [NARROW_RING]
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC + 4);
     int* s_offs = reinterpret_cast<int*>(smem + OFF_TABLE);
@@ -204,6 +209,7 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             mbar_init(empty_bar + i, 1);
         }
         for (int i = 0; i < 2; ++i) { mbar_init(part_full + i, 1); mbar_init(part_empty + i, 16); }
+        for (int i = 0; i < NARROW_RING; ++i) { mbar_init(nar_full + i, 1); mbar_init(nar_empty + i, 16); }
         *abort_flag = 0;
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
@@ -278,11 +284,26 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             uint32_t step = 0;   // only its two low bits matter (buffer and phase)
             bool ok = true;
             for (int t = pair_id; t < tw.items && ok; t += num_pairs) {
-                const uint32_t idesc = t >= tw.full ? idesc_narrow : idesc_full;
+                // A narrow piece is always a pair's last item (there are at most as many as pairs).  Its partial products
+                // go through a ring of four 64-column buffers of their own barriers: with the short MMA the round trip
+                // MMA -> promotion -> "buffer free" would otherwise set the pace.  The four buffers lie in the columns
+                // of full-width buffer 0, so its last reader must have finished first.
+                const bool narrow = t >= tw.full;
+                if (narrow) {
+                    const uint32_t next0 = (step + 1u) & ~1u;   // the step that would use buffer 0 next
+                    if (!mbar_wait_cluster(part_empty + 0, ((next0 >> 1) & 1u) ^ 1u, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    step = 0;
+                }
+                const uint32_t idesc = narrow ? idesc_narrow : idesc_full;
+                uint64_t* acc_full = narrow ? nar_full : part_full;
+                uint64_t* acc_empty = narrow ? nar_empty : part_empty;
+                const uint32_t ring = narrow ? NARROW_RING : 2;
+                const uint32_t ring_shift = narrow ? 2 : 1;
+                const uint32_t buf_cols = narrow ? NARROW_N : TILE_N;
                 for (int kb = 0; kb < num_kb; ++kb, ++step) {
-                    const int p = static_cast<int>(step & 1);
-                    const uint32_t pphase = (step >> 1) & 1u;
-                    if (!mbar_wait_cluster(part_empty + p, pphase ^ 1u, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    const uint32_t p = step & (ring - 1u);
+                    const uint32_t pphase = (step >> ring_shift) & 1u;
+                    if (!mbar_wait_cluster(acc_empty + p, pphase ^ 1u, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     if (!mbar_wait(full_bar + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     if (!mbar_wait_cluster(peer_full + stage, phase, abort_flag, ST_TIMEOUT_MMA)) { ok = false; break; }
                     tc_fence_after();
@@ -291,9 +312,9 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                     if (elect_one()) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            mma_f8f6f4_pair(tmem_base + p * TILE_N, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+                            mma_f8f6f4_pair(tmem_base + p * buf_cols, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
                         tc_commit_pair(empty_bar + stage);
-                        tc_commit_pair(part_full + p);
+                        tc_commit_pair(acc_full + p);
                     }
                     __syncwarp();
                     if (++stage == NUM_STAGES) { stage = 0; phase ^= 1u; }
@@ -321,13 +342,15 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         bool ok = true;
         for (int t = pair_id; t < tw.items && ok; t += num_pairs) {
             const Tile ti = tw.decode(t);
-            // full width: 128 columns per warp; a 64-column piece: 32 per warp
-            if (ti.width == TILE_N)
-                ok = promote_tile<SB_BLOCK, ACT, TILE_N / 32>(args, ti, num_kb, nb128, tmem_base, part_full, part_empty, abort_flag, step,
-                                                              static_cast<int>(rank), quad, half, lane);
-            else
-                ok = promote_tile<SB_BLOCK, ACT, NARROW_N / 32>(args, ti, num_kb, nb128, tmem_base, part_full, part_empty, abort_flag,
-                                                                step, static_cast<int>(rank), quad, half, lane);
+            // full width: 128 columns per warp, two buffers; a 64-column piece (a pair's last item): 32 per warp, its own ring
+            if (ti.width == TILE_N) {
+                ok = promote_tile<SB_BLOCK, ACT, TILE_N / 32, 2>(args, ti, num_kb, nb128, tmem_base, part_full, part_empty, abort_flag,
+                                                                 step, static_cast<int>(rank), quad, half, lane);
+            } else {
+                uint32_t nstep = 0;
+                ok = promote_tile<SB_BLOCK, ACT, NARROW_N / 32, NARROW_RING>(args, ti, num_kb, nb128, tmem_base, nar_full, nar_empty,
+                                                                             abort_flag, nstep, static_cast<int>(rank), quad, half, lane);
+            }
         }
     }
 
