@@ -10,6 +10,12 @@
 // while the tensor cores fill the other buffer.  The promotion streams tensor memory in 16-column
 // pieces, the next piece in flight while the current one is multiplied.
 //
+// Tiles are dealt to the CTA pairs round robin.  The tiles left over after the last full round are cut
+// into four 64-column pieces each when all pieces fit into one round (Walker::plan): a piece is a
+// pair's last item, multiplies with N = 64 from a tensor map with a 32-row box, and its partial
+// products pass through four 64-column buffers with barriers of their own.  The K order per output
+// element is unchanged, so the result is bit-identical to the uncut schedule.
+//
 //   warp 0     TMA producer          warp 1   leader: MMA issuer / peer: "stage landed" forwarder
 //   warps 2-9  promotion + epilogue: warp w owns lanes 32*(w%4).. and 128 of the 256 columns
 #include <cuda_bf16.h>
