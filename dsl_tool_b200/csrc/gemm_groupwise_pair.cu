@@ -222,6 +222,18 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         prefetch_tmap(&tmap_b);
         prefetch_tmap(&tmap_b_narrow);
     }
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) tmem_alloc_pair(tmem_ptr, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    // Everything above touches no global memory, so under programmatic stream serialisation it runs while the
+    // preceding kernel of the stream (the activation quantiser) drains; from here on that kernel's results are read.
+    griddep_wait();
     for (int g = threadIdx.x; g <= groups; g += blockDim.x)
         s_offs[g] = args.group_offsets != nullptr ? args.group_offsets[g] : (g == 0 ? 0 : args.m_total);
     __syncthreads();
@@ -235,13 +247,6 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         s_tile0[groups] = t;
     }
     __syncthreads();
-    cluster_sync_all();
-    if (warp == 1) tmem_alloc_pair(tmem_ptr, TMEM_COLS);
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_ptr;
 
     Walker tw;
     tw.offs = s_offs;
@@ -405,8 +410,21 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     if (max_tiles > (1ll << 29)) return DSL_ERR_SHAPE;   // tile counters in the kernel are 32-bit
     long long clusters = max_tiles < max_clusters ? max_tiles : max_clusters;
     if (clusters < 1) clusters = 1;
-    gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT><<<static_cast<unsigned>(2 * clusters), gwp::THREADS, gwp::SMEM_BYTES, st>>>(ta, tb, tbn, args);
-    return static_cast<int>(cudaGetLastError());
+    // Launched with programmatic stream serialisation: the grid's set-up overlaps the tail of the preceding kernel
+    // of the stream when that kernel allows it (the quantisers do); the kernel's griddep_wait() guards the rest.
+    // DSLGEMM_PDL=0 launches it the plain way (for measurements).
+    static const bool pdl = [] { const char* e = getenv("DSLGEMM_PDL"); return !(e != nullptr && e[0] == '0'); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    cfg.blockDim = dim3(gwp::THREADS);
+    cfg.dynamicSmemBytes = gwp::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>, ta, tb, tbn, args));
 }
 
 int launch_gemm_fp8_groupwise_pair(const void* A, const void* B, GemmArgs args, cudaStream_t st) {

@@ -196,6 +196,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 quant_fp8_1x128_kernel(const T* __restrict__ x, long long M, int K, uint8_t* __restrict__ q,
                        float* __restrict__ scales, int log2_cp) {
+    griddep_launch_dependents();   // the GEMM that follows may set itself up now; it waits before reading q / scales
     const int cpr = K / 16;
     const int ng = (K + 127) / 128;
     const long long row = blockIdx.x * static_cast<long long>(256 >> log2_cp) + (threadIdx.x >> log2_cp);
