@@ -219,6 +219,34 @@ def test_grouped_ragged_experts(cuda_device, fmt, skew):
     assert rel_frobenius(got.cpu().numpy(), want) <= REL_FROB_TOL
 
 
+def test_grouped_fp8_groupwise_last_round_cut(cuda_device):
+    """Row groups of 700, 0, 1300 and 290 rows = 3 + 0 + 6 + 2 row tiles x 8 column tiles = 88 tiles on 74 CTA pairs:
+    the 14 tiles after the full round run as 64-column pieces, across group boundaries and ragged row tails.  Each
+    group must match the oracle and equal, bit for bit, the same rows multiplied as a dense problem of their own."""
+    from dsl_tool_b200 import grouped_gemm, fp8_gemm
+    rng = np.random.default_rng(77)
+    N, K = 2048, 384
+    offs = np.array([0, 700, 700, 2000, 2290], np.int32)
+    G, M = len(offs) - 1, int(offs[-1])
+    a = torch.from_numpy(activations(rng, M, K)).bfloat16()
+    w = torch.from_numpy(weights(rng, G * N, K).reshape(G, N, K)).bfloat16()
+    ao, wo = a.float().numpy(), w.float().numpy()
+    got = grouped_gemm(a.cuda(), w.cuda(), G, torch.from_numpy(offs).cuda(), format="fp8_groupwise", b_layout="nk",
+                       out_dtype="float32")
+    _status_ok()
+    qa, sa = O.quant_fp8_groupwise(ao)
+    for g in range(G):
+        r0, r1 = int(offs[g]), int(offs[g + 1])
+        if r1 == r0:
+            continue
+        qb, sbb = O.quant_fp8_block(wo[g])
+        want = O.gemm_fp8_groupwise(qa[r0:r1], qb, sa[r0:r1], O.expand_block_scale(sbb, N))
+        assert rel_frobenius(got[r0:r1].cpu().numpy(), want) <= REL_FROB_TOL
+        alone = fp8_gemm(a[r0:r1].cuda(), w[g].cuda(), mode="groupwise", b_layout="nk")
+        _status_ok()
+        assert torch.equal(got[r0:r1], alone.float())
+
+
 def test_run_to_run_determinism(cuda_device):
     from dsl_tool_b200 import fp4_gemm
     rng = np.random.default_rng(41)
