@@ -17,7 +17,7 @@
 // element is unchanged, so the result is bit-identical to the uncut schedule.
 //
 //   warp 0     TMA producer          warp 1   leader: MMA issuer / peer: "stage landed" forwarder
-//   warps 2-9  promotion + epilogue: warp w owns lanes 32*(w%4).. and 128 of the 256 columns
+//   warps 2-9  promotion + epilogue: warp w owns lanes 32*(w%4).. and 128 of the 256 columns (32 of a piece's 64)
 #include <cuda_bf16.h>
 #include <stdio.h>
 #include <stdlib.h>
