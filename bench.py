@@ -327,7 +327,8 @@ def run_reference(args):
         "impl": "reference", "metric": "gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_NAME[cfg["kind"]], "data": "synthetic",
-        "config": {"workload": args.workload, "note": "CPU port of the reference emulation (oracle), bounded sample"},
+        "config": {"workload": args.workload, **{k: cfg[k] for k in ("M", "K", "N") if k in cfg},
+                   "note": "CPU port of the reference emulation (oracle), bounded sample"},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
