@@ -72,6 +72,21 @@ def test_dense_swiglu(cuda_device, fmt, M, H):
         assert rel_frobenius(got.cpu().numpy(), (g / (1 + np.exp(-g))) * u) <= 1e-5
 
 
+def test_groupwise_swiglu_with_the_last_round_cut(cuda_device):
+    """2560 x 2048 gate/up columns = 80 tiles on 74 CTA pairs: the tiles after the full round run as 64-column
+    pieces, i.e. 32 (gate, up) pairs each, through the activation epilogue of the group-scaled FP8 kernel."""
+    rng = np.random.default_rng(2560)
+    M, H, K = 2560, 1024, 256
+    a = torch.from_numpy(activations(rng, M, K, outliers=True)).bfloat16()
+    w = torch.from_numpy(weights(rng, 2 * H, K, std=0.05)).bfloat16()
+    pw = D.pack_weight(w.cuda(), "fp8_block128", gate_up_interleave=True)
+    got = D.linear(a.cuda(), pw, activation="swiglu")
+    want = _swiglu_of_interleaved(_oracle_gemm("fp8_block128", a.float().numpy(), _interleave(w.float().numpy())))
+    assert tuple(got.shape) == (M, H) and rel_frobenius(got.cpu().numpy(), want) <= REL_FROB_TOL
+    alone = D.linear(a[-256:].cuda(), pw, activation="swiglu")             # 8 tiles, nothing cut: the same bits
+    assert torch.equal(got[-256:], alone)
+
+
 @pytest.mark.parametrize("fmt", ["nvfp4", "fp8_groupwise", "bf16"])
 def test_grouped_swiglu_ragged_experts(cuda_device, fmt):
     rng = np.random.default_rng(12)
