@@ -83,6 +83,7 @@ _SIGNATURES = {
     "dsl_moe_combine": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),
+    "dsl_selftest_groupwise_schedule": (_i, [_vp, _i, _ll, _i, _i, _i, _i, _vp, _i]),
 }
 
 

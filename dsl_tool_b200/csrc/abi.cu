@@ -181,4 +181,21 @@ int dsl_selftest_bounded_wait(uint32_t* status, unsigned limit_us, void* stream)
     return launch_bounded_wait_selftest(status, limit_us, as_stream(stream));
 }
 
+int dsl_selftest_groupwise_schedule(const int32_t* group_offsets, int num_groups, long long m_total, int N, int pairs,
+                                    int band, int whole_tiles_only, int32_t* out, int max_items) {
+    if (out == nullptr) return DSL_ERR_NULL;
+    if (m_total < 0 || m_total > 0x7FFFFFFF || N <= 0 || pairs <= 0 || max_items < 0) return DSL_ERR_SHAPE;
+    if (group_offsets != nullptr) {
+        if (num_groups < 1 || num_groups > DSL_MAX_GROUPS || group_offsets[0] != 0 || group_offsets[num_groups] != m_total)
+            return DSL_ERR_SHAPE;
+        for (int g = 0; g < num_groups; ++g)
+            if (group_offsets[g + 1] < group_offsets[g]) return DSL_ERR_SHAPE;
+    }
+    const long long tiles = ((m_total + 255) / 256 + (group_offsets != nullptr ? num_groups : 0)) * ((N + 255LL) / 256);
+    if (tiles > (1ll << 29)) return DSL_ERR_SHAPE;
+    const int n = groupwise_pair_schedule_host(group_offsets, num_groups, static_cast<int>(m_total), N, pairs, band,
+                                               whole_tiles_only, out, max_items);
+    return n < 0 ? DSL_ERR_TOO_LARGE : n;
+}
+
 }  // extern "C"

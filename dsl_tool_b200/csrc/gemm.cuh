@@ -54,6 +54,8 @@ int choose_split_k(const GemmArgs& args, long long tiles);
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);
 int launch_gemm_pair(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);
 int launch_gemm_fp8_groupwise_pair(const void* A, const void* B, GemmArgs args, cudaStream_t st);
+int groupwise_pair_schedule_host(const int* group_offsets, int groups, int m_total, int n, int pairs, int band, int whole_tiles_only,
+                                 int* out, int max_items);
 int launch_gemm_fp8_groupwise(const void* A, const void* B, GemmArgs args, cudaStream_t st);
 int launch_bounded_wait_selftest(uint32_t* status, unsigned limit_us, cudaStream_t st);
 bool make_tmap_u8(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box0,

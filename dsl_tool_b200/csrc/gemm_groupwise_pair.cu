@@ -64,12 +64,12 @@ struct Walker {
     // The tiles left over after the last full round of the grid would keep a few CTA pairs busy for a whole
     // tile time while the others idle; when all their 64-column pieces fit into one round they are cut up.
     // Every output element still sums the same K groups in the same order, so the result does not change.
-    __device__ __forceinline__ void plan(int pairs) {
+    __host__ __device__ __forceinline__ void plan(int pairs) {
         const int rest = total % pairs;
         full = (total > pairs && rest > 0 && rest * NARROW_PARTS <= pairs) ? total - rest : total;
         items = full + (total - full) * NARROW_PARTS;
     }
-    __device__ __forceinline__ Tile decode(int item) const {
+    __host__ __device__ __forceinline__ Tile decode(int item) const {
         int t = item, part = 0, width = TILE_N;
         if (item >= full) {
             const int q = item - full;
@@ -81,7 +81,7 @@ struct Walker {
         const int b = t / per_band;
         const int r = t - b * per_band;
         const int nb0 = b * band;
-        const int wb = min(band, n_tiles - nb0);
+        const int wb = band < n_tiles - nb0 ? band : n_tiles - nb0;
         const int mt = r / wb;
         const int nt = nb0 + (r - mt * wb);
         int lo = 0, hi = groups;
@@ -425,6 +425,45 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>, ta, tb, tbn, args));
+}
+
+// The kernel's work list, computed on the host with the kernel's own Walker (no CUDA call): item i of the launch goes
+// to CTA pair i % pairs and is written as six ints {pair, group, row0, row_end, n0, width}.  Returns the number of
+// items, or -1 when `max_items` is too small.  For tests of the schedule (every output element covered exactly once).
+int groupwise_pair_schedule_host(const int* group_offsets, int groups, int m_total, int n, int pairs, int band, int whole_tiles_only,
+                                 int* out, int max_items) {
+    using namespace gwp;
+    const int one[2] = {0, m_total};
+    const int* offs = group_offsets != nullptr ? group_offsets : one;
+    if (group_offsets == nullptr) groups = 1;
+    int* tile0 = static_cast<int*>(malloc(sizeof(int) * (groups + 1)));
+    if (tile0 == nullptr) return -1;
+    int t = 0;
+    for (int g = 0; g < groups; ++g) {
+        tile0[g] = t;
+        const int rows = offs[g + 1] - offs[g];
+        if (rows > 0) t += (rows + TILE_M - 1) / TILE_M;
+    }
+    tile0[groups] = t;
+    Walker tw;
+    tw.offs = offs;
+    tw.tile0 = tile0;
+    tw.groups = groups;
+    tw.m_tiles = t;
+    tw.n_tiles = (n + TILE_N - 1) / TILE_N;
+    tw.band = band < 1 ? 8 : band;
+    tw.total = tw.m_tiles * tw.n_tiles;
+    tw.plan(pairs);
+    if (whole_tiles_only) { tw.full = tw.total; tw.items = tw.total; }
+    int count = tw.items;
+    if (count > max_items) count = -1;
+    for (int i = 0; i < count; ++i) {
+        const Tile ti = tw.decode(i);
+        int* o = out + 6 * i;
+        o[0] = i % pairs; o[1] = ti.group; o[2] = ti.row0; o[3] = ti.row_end; o[4] = ti.n0; o[5] = ti.width;
+    }
+    free(tile0);
+    return count;
 }
 
 int launch_gemm_fp8_groupwise_pair(const void* A, const void* B, GemmArgs args, cudaStream_t st) {

@@ -230,6 +230,16 @@ int dsl_gemm_fp4_static_scratch(const uint8_t* A, const uint8_t* B, const uint8_
  * faulting or hanging the device. */
 int dsl_selftest_bounded_wait(uint32_t* status, unsigned limit_us, void* stream);
 
+/* The work list of the group-scaled FP8 CTA-pair kernel for a problem, computed on the HOST by the kernel's own
+ * scheduler code (no CUDA call, no GPU needed): for tests that every output element is covered exactly once.
+ * group_offsets: HOST int32 [num_groups + 1] row offsets, or NULL for one dense group of m_total rows.  pairs = CTA
+ * pairs of the launch (74 on a 148-SM part), band <= 0 = the default raster band, whole_tiles_only = 1 switches the
+ * cutting of the last round off.  Item i (it runs on pair i % pairs, in order) is written to out[6 i ..] as
+ * {pair, group, row0, row_end, n0, width}: rows [row0, min(row0 + 256, row_end)) x columns [n0, min(n0 + width, N)).
+ * Returns the number of items, DSL_ERR_TOO_LARGE when it exceeds max_items, or another DSL_ERR_*. */
+int dsl_selftest_groupwise_schedule(const int32_t* group_offsets, int num_groups, long long m_total, int N, int pairs,
+                                    int band, int whole_tiles_only, int32_t* out, int max_items);
+
 #ifdef __cplusplus
 }
 #endif
