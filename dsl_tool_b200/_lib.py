@@ -19,10 +19,12 @@ LIB_PATH = os.environ.get("DSLGEMM_LIBRARY", os.path.join(_HERE, "libdslgemm.so"
 F32, BF16, F16 = 0, 1, 2
 FP8_PER_TENSOR, FP8_GROUP_1X128, FP8_BLOCK_128X128 = 0, 1, 2
 FP4_NV, FP4_MX = 0, 1
+OP_GEMM_FP8, OP_GEMM_BF16, OP_GEMM_FP4_NV, OP_GEMM_FP4_MX, OP_GEMM_FP8_GROUPWISE = 0, 1, 2, 3, 4
 ACT_NONE, ACT_SWIGLU, ACT_GEGLU = 0, 1, 2
 OUT_NVFP4 = 3
 MAX_GROUPS = 1024
 STATIC_SCRATCH_BYTES = 4 << 20
+WS_HEADER_BYTES = 64 << 10
 
 _ERR_NAMES = {
     -1: "a required pointer is NULL",
@@ -73,6 +75,7 @@ _SIGNATURES = {
                           ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_gemm_fp4_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i,
                                          ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_workspace_bytes": (ctypes.c_size_t, [_i, _ll, _i, _i, _i]),
     "dsl_quant_fp4_ref32": (_i, [_vp, _i, _ll, _vp, _vp, _vp]),
     "dsl_gemm_fp4_ref32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dsl_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
@@ -82,6 +85,7 @@ _SIGNATURES = {
     "dsl_moe_dispatch_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _ll, _i, _i, _vp, _vp]),
     "dsl_moe_combine": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
+    "dsl_selftest_static_scratch_copy": (_i, [_vp, ctypes.c_size_t, ctypes.c_size_t, _i, _vp]),
     "dsl_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),
     "dsl_selftest_groupwise_schedule": (_i, [_vp, _i, _ll, _i, _i, _i, _i, _vp, _i]),
 }
@@ -172,14 +176,18 @@ _workspace: Dict[tuple, torch.Tensor] = {}
 WORKSPACE_BYTES = 16 << 20
 
 
-def workspace(device: torch.device) -> torch.Tensor:
-    """Split-K scratch, one buffer per (device, stream): launches on one stream use it in
-    order, launches on different streams never share it."""
+def workspace(device: torch.device, need: int = WORKSPACE_BYTES) -> Optional[torch.Tensor]:
+    """Scratch for partial sums along K, one buffer per (device, stream): launches on one stream use
+    it in order, launches on different streams never share it.  `need` is what dsl_workspace_bytes()
+    reports for the problem: 0 gives None (the kernels serving it use no scratch), anything else a
+    buffer of at least that size (it only ever grows)."""
+    if need <= 0:
+        return None
     idx = device.index if device.index is not None else torch.cuda.current_device()
     key = (idx, torch.cuda.current_stream(device).cuda_stream)
     t = _workspace.get(key)
-    if t is None:
-        t = torch.empty(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+    if t is None or t.numel() < need:
+        t = torch.empty(max(int(need), WORKSPACE_BYTES), dtype=torch.uint8, device=device)
         _workspace[key] = t
     return t
 

@@ -85,8 +85,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
     }
-    for (int g = threadIdx.x; g <= groups; g += blockDim.x)
-        s_offs[g] = args.group_offsets != nullptr ? args.group_offsets[g] : (g == 0 ? 0 : args.m_total);
+    load_group_offsets(s_offs, args.group_offsets, groups, args.m_total);
     if (C::SF_ATOMS > 0) {   // never let an uninitialised (possibly NaN) scale byte meet zero-filled data
         uint32_t* z = reinterpret_cast<uint32_t*>(smem + C::OFF_SFA);
         for (int i = threadIdx.x; i < C::NUM_STAGES * (C::SFA_STAGE + C::SFB_STAGE) / 4; i += blockDim.x) z[i] = 0u;
@@ -97,7 +96,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         int t = 0;
         for (int g = 0; g < groups; ++g) {
             s_tile0[g] = t;
-            const int rows = s_offs[g + 1] - s_offs[g];
+            const int rows = monotone_rows(s_offs, g);
             t += rows > 0 ? (rows + BLOCK_M - 1) / BLOCK_M : 0;
         }
         s_tile0[groups] = t;
@@ -400,13 +399,17 @@ bool make_tmap_u8(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, ui
     return r == CUDA_SUCCESS;
 }
 
-static int sm_count() {
-    static int n = []() {
-        int dev = 0, v = 0;
-        cudaGetDevice(&dev);
+int sm_count() {
+    static PerDeviceInt cache;   // 0 = not asked yet
+    const int dev = current_device_slot();
+    if (dev < 0) return 148;
+    int n = cache.v[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        int v = 0;
         cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-        return v > 0 ? v : 148;
-    }();
+        n = v > 0 ? v : 148;
+        cache.v[dev].store(n, std::memory_order_relaxed);
+    }
     return n;
 }
 
@@ -417,11 +420,13 @@ static int launch_one(const void* A, const void* B, const GemmArgs& args, long l
     if (!make_tmap_u8(&ta, A, args.k_bytes, args.m_total, 0, STAGE_KB, BLOCK_M)) return DSL_ERR_DRIVER;
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
     if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, BLOCK_N)) return DSL_ERR_DRIVER;
-    static bool attr_set = false;   // idempotent; a race here only repeats the same call
-    if (!attr_set) {
+    static PerDeviceInt attr_set;   // per device; idempotent, a race here only repeats the same call
+    const int dev = current_device_slot();
+    if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
+    if (attr_set.v[dev].load(std::memory_order_acquire) == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
-        attr_set = true;
+        attr_set.v[dev].store(1, std::memory_order_release);
     }
     const long long items = max_tiles * (args.split_k > 1 ? args.split_k : 1);
     long long grid = items < sm_count() ? items : sm_count();
@@ -462,6 +467,37 @@ int choose_split_k(const GemmArgs& args, long long tiles) {
     return (num_kb + kb_per - 1) / kb_per;   // every slice non-empty
 }
 
+// Tile shape of the 1-CTA kernel for a problem: 128-wide tiles (two accumulator stages, more CTAs in
+// flight) for narrow outputs and whenever 256-wide tiles would leave most SMs without work.
+static bool one_cta_tiles(const GemmArgs& args, long long* max_tiles) {
+    const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
+    const long long m_tiles_max = (args.m_total + BLOCK_M - 1) / BLOCK_M + groups - 1;
+    const bool narrow = args.n <= 128 || (args.n % 256 != 0 && args.n % 256 <= 128 && args.n < 1024) ||
+                        m_tiles_max * ((args.n + 255) / 256) * 2 <= sm_count();
+    const int block_n = narrow ? 128 : 256;
+    *max_tiles = m_tiles_max * ((args.n + block_n - 1) / block_n);
+    return narrow;
+}
+
+// Bytes of caller workspace (header included) that launch_gemm would put to use for this problem on
+// the current device; 0 when the kernels that serve it need none.  `args.partial` must be non-null
+// with a generous `partial_bytes` so that the same decisions are taken as in a real launch.
+size_t gemm_workspace_bytes(int kind, const GemmArgs& args) {
+    if (args.m_total <= 0 || args.n <= 0) return 0;
+    const int forced = forced_kernel();
+    if (forced == 0 || forced == 3) {
+        bool served = false;
+        const size_t b = decode_scratch_bytes(kind, args, &served);
+        if (served) return b > 0 ? b + DSL_WS_HEADER_BYTES : 0;
+    }
+    if (forced == 2 || (forced == 0 && args.m_total > 128 && args.n >= 256)) return 0;
+    long long max_tiles = 0;
+    one_cta_tiles(args, &max_tiles);
+    const int split_k = choose_split_k(args, max_tiles);
+    if (split_k <= 1) return 0;
+    return DSL_WS_HEADER_BYTES + static_cast<size_t>(split_k) * args.m_total * args.n * sizeof(float);
+}
+
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st) {
     if (args.m_total <= 0 || args.n <= 0) return 0;
     const int forced = forced_kernel();
@@ -470,16 +506,8 @@ int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStrea
         if (rc != DSL_NOT_SERVED) return rc;
     }
     if (forced == 2 || (forced == 0 && args.m_total > 128 && args.n >= 256)) return launch_gemm_pair(kind, A, B, args, st);
-    const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
-    // Narrow outputs get 128-wide tiles (two accumulator stages, more CTAs in flight).
-    const long long m_tiles_max = (args.m_total + BLOCK_M - 1) / BLOCK_M + groups - 1;
-    // 128-wide tiles (two accumulator stages, more CTAs in flight) for narrow outputs and
-    // whenever 256-wide tiles would leave most SMs without work.
-    const bool narrow = args.n <= 128 || (args.n % 256 != 0 && args.n % 256 <= 128 && args.n < 1024) ||
-                        m_tiles_max * ((args.n + 255) / 256) * 2 <= sm_count();
-    const int block_n = narrow ? 128 : 256;
-    const long long n_tiles = (args.n + block_n - 1) / block_n;
-    const long long max_tiles = m_tiles_max * n_tiles;
+    long long max_tiles = 0;
+    const bool narrow = one_cta_tiles(args, &max_tiles);
     if (args.band <= 0) args.band = 8;
     // Few tiles and a long K (decode shapes): cut K so that every SM streams part of the weight.
     // Dense problems only; needs caller scratch for the fp32 partial sums.

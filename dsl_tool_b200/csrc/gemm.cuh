@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "dslgemm.h"
 
 namespace dsl {
@@ -35,8 +37,10 @@ struct GemmArgs {
     int band;                    // column tiles per raster band (L2 reuse)
     int whole_tiles_only;        // 1: the tiles after the last full round are not cut into narrow pieces (measurements)
     int split_k;                 // > 1: K is cut into this many slices whose fp32 partial sums go to `partial`
-    float* partial;              // [split_k, m_total, n] scratch (dense problems only)
+    float* partial;              // [split_k, m_total, n] scratch (dense problems only): the caller's workspace
+                                 // after its first DSL_WS_HEADER_BYTES
     size_t partial_bytes;        // capacity of `partial`
+    unsigned long long* ws_words;   // the workspace's header: DSL_WS_HEADER_BYTES / 8 arrival words (gemm_decode.cu)
     int b_static;                // B was complete before the preceding kernel of the stream was launched
     int act;                     // DSL_ACT_*: SWIGLU turns column pairs (gate, up) into one output column
     uint8_t* out_sf;             // non-null: the result is quantised to NVFP4 (c = packed bytes, out_sf = scale tiles)
@@ -46,10 +50,34 @@ struct GemmArgs {
     uint32_t* status;
 };
 
+// A caller's workspace starts with a header that only the weight-streaming kernel's arrival words ever
+// occupy (one 64-bit word per 128-column tile, tagged with a per-launch epoch); partial sums of every
+// kernel start behind it.  Because the words sit at the same place whatever the problem's shape, no
+// call can leave floating-point data where a later call looks for its words.
+constexpr size_t DSL_WS_HEADER_BYTES = 64 * 1024;
+
+// State that belongs to a device's context (function attributes, occupancy, SM count) is kept per
+// device: one process may drive several GPUs.
+constexpr int DSL_MAX_DEVICES = 64;
+struct PerDeviceInt {
+    std::atomic<int> v[DSL_MAX_DEVICES];
+};
+// Index of the current device, or -1 when it cannot serve as an index of PerDeviceInt.
+inline int current_device_slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= DSL_MAX_DEVICES) return -1;
+    return dev;
+}
+int sm_count();   // of the current device
+
 constexpr int DSL_DECODE_MAX_ROWS = 128;   // activation rows the weight-streaming kernel (gemm_decode.cu) takes
 constexpr int DSL_NOT_SERVED = -1000;      // launch_gemm_decode: problem outside its domain, use the tiled kernels
 
 int launch_gemm_decode(int kind, const void* A, const void* B, const GemmArgs& args, cudaStream_t st);
+// Scratch bytes (behind the header) the weight-streaming kernel would use for this problem; 0 when it
+// combines inside clusters or does not serve the problem (*served says which).
+size_t decode_scratch_bytes(int kind, const GemmArgs& args, bool* served);
+size_t gemm_workspace_bytes(int kind, const GemmArgs& args);
 int choose_split_k(const GemmArgs& args, long long tiles);
 int launch_gemm(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);
 int launch_gemm_pair(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st);

@@ -14,8 +14,11 @@
 //     Otherwise (more tiles than SMs, many tokens) runs may cross tile borders: a run that covers
 //     a whole tile writes C directly; a partial one goes to scratch (at most two per CTA) and is
 //     counted on the tile's arrival word, and the CTA that arrives last adds the tile's partials
-//     in ascending K order.  Nobody waits for anybody; arrival words carry a per-launch epoch, so
-//     scratch needs no initialisation.  Both ways the result is identical from run to run.
+//     in ascending K order.  Nobody waits for anybody.  The arrival words are the one part of the
+//     scratch that is read before it is written: they live in the workspace's header, where no kernel
+//     ever stores anything else, carry a per-launch epoch (a word of another epoch counts as empty) and
+//     are zeroed by the CTA that finishes the tile, so scratch needs no initialisation.  Both ways the
+//     result is identical from run to run.
 //   * The kernel is launched with programmatic stream serialisation: set-up, and for a weight
 //     the caller declares static also the first ring of weight tiles, overlap the tail of the
 //     preceding kernel (the activation quantiser); everything else waits for it.
@@ -26,6 +29,7 @@
 #include <stdlib.h>
 
 #include <atomic>
+#include <chrono>
 
 #include "gemm.cuh"
 #include "gemm_tiles.cuh"
@@ -75,8 +79,9 @@ struct DecPlan {
     long long units;      // n_tiles * num_kb
     int ctas;             // grid size; CTA c owns units [c*units/ctas, (c+1)*units/ctas)
     int cluster_runs;     // > 1: cluster mode, this many consecutive CTAs share one tile; 0: scratch mode
-    unsigned long long* arrivals;   // scratch mode: one word per column tile, (epoch << 16) | partials delivered
-    unsigned long long epoch;       // differs from launch to launch (never 0)
+    unsigned long long* arrivals;   // scratch mode: one word per column tile in the workspace header,
+                                    // (epoch << 16) | partials delivered
+    unsigned long long epoch;       // differs from launch to launch (never 0), 48 bits
 };
 
 // First unit of CTA c.  Evaluated once per CTA index into a shared-memory table at kernel start.
@@ -532,16 +537,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 }
 
 // ---- host side ---------------------------------------------------------------------------
-static int dec_sm_count() {
-    static int n = []() {
-        int dev = 0, v = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-        return v > 0 ? v : 148;
-    }();
-    return n;
-}
-
 // DSLGEMM_DECODE_CTAS=<n> forces scratch mode with that grid size, DSLGEMM_DECODE_CLUSTER=0 disables
 // cluster mode (for measurements).
 static int env_int(const char* name, int fallback) {
@@ -549,21 +544,44 @@ static int env_int(const char* name, int fallback) {
     return e != nullptr ? atoi(e) : fallback;
 }
 
+// Arrival words carry a per-launch epoch in their upper 48 bits.  Epochs count up from a start value
+// drawn once per process from the clock and the address-space layout, so that stale bytes a caller's
+// workspace happens to hold (it need not be cleared) match the current epoch only by a 2^-48 accident,
+// not because both are small integers.
+static unsigned long long next_epoch() {
+    static std::atomic<unsigned long long> source{[] {
+        unsigned long long x = static_cast<unsigned long long>(std::chrono::steady_clock::now().time_since_epoch().count());
+        x ^= static_cast<unsigned long long>(reinterpret_cast<uintptr_t>(&x)) << 17;
+        x += 0x9E3779B97F4A7C15ull;                      // splitmix64 finaliser
+        x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+        x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+        return x ^ (x >> 31);
+    }()};
+    unsigned long long e;
+    do { e = source.fetch_add(1) & 0xFFFFFFFFFFFFull; } while (e == 0);
+    return e;
+}
+
+// Grid, combine mode and scratch need of a problem.  Returns false when this kernel does not serve it.
+// `scratch_needed` is what the plan would like to have behind the workspace header (0 in cluster mode);
+// with less the grid shrinks (`plan.ctas`), with none the problem is not served.
 template <int KIND, int TOK>
-static int launch_decode_one(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
+static bool plan_decode(const GemmArgs& args, DecPlan& plan, size_t* scratch_needed) {
     using C = DecCfg<KIND, TOK>;
     static const int forced_ctas = env_int("DSLGEMM_DECODE_CTAS", 0);
     static const int allow_cluster = env_int("DSLGEMM_DECODE_CLUSTER", 1);
-    DecPlan plan = {};
+    plan = DecPlan{};
+    *scratch_needed = 0;
     plan.n_tiles = (args.n + 127) / 128;
     plan.num_kb = (args.k_bytes + STAGE_KB - 1) / STAGE_KB;
     plan.units = static_cast<long long>(plan.n_tiles) * plan.num_kb;
-    if (plan.units > 0x7FFFFFFFll) return DSL_NOT_SERVED;
-    const int sms = dec_sm_count();
+    if (plan.units > 0x7FFFFFFFll) return false;
+    const int sms = sm_count();
     // Grid.  Few column tiles: every tile is cut into the same number of K runs (each CTA works inside one
     // tile); with 2 or 4 runs (and room for the peers' partial tiles) the CTAs of a tile form a cluster.
     // More tiles than SMs: one CTA per SM and the runs cross tile borders.  Every CTA streams at least four
-    // stages.  Scratch mode keeps two partial tiles per CTA and one arrival word per column tile in scratch.
+    // stages.  Scratch mode keeps two partial tiles per CTA behind the workspace header and one arrival word
+    // per column tile inside it.
     long long ctas = sms;
     int cluster_runs = 0;
     if (plan.n_tiles <= sms) {
@@ -581,29 +599,42 @@ static int launch_decode_one(const void* A, const void* B, const GemmArgs& args,
     if (ctas > DEC_MAX_CTAS) { ctas = DEC_MAX_CTAS; cluster_runs = 0; }
     // More than 32 tokens: only the cluster combine is fast enough (the scratch combine walks the rows with
     // one L2 round trip after the other); otherwise the tiled split-K kernel takes the problem.
-    if (TOK > 32 && cluster_runs == 0) return DSL_NOT_SERVED;
-    if (cluster_runs == 0) {
-        const size_t words_bytes = static_cast<size_t>(plan.n_tiles) * sizeof(unsigned long long);
+    if (TOK > 32 && cluster_runs == 0) return false;
+    if (ctas < 1) return false;
+    // every run a whole number of tiles (one CTA per tile, or fewer CTAs than tiles dividing them evenly):
+    // each CTA writes C itself and nothing passes through scratch
+    const bool whole_only = cluster_runs == 0 && plan.units % ctas == 0 && (plan.units / ctas) % plan.num_kb == 0;
+    if (cluster_runs == 0 && !whole_only) {
+        if (static_cast<size_t>(plan.n_tiles) * sizeof(unsigned long long) > DSL_WS_HEADER_BYTES) return false;
         const size_t per_cta = 2ull * TOK * 128 * sizeof(float);
-        const long long by_scratch = args.partial_bytes > words_bytes ? static_cast<long long>((args.partial_bytes - words_bytes) / per_cta) : 0;
+        *scratch_needed = per_cta * static_cast<size_t>(ctas);
+        const long long by_scratch = args.partial != nullptr ? static_cast<long long>(args.partial_bytes / per_cta) : 0;
         if (ctas > by_scratch) ctas = by_scratch;
-        if (ctas < 1) return DSL_NOT_SERVED;    // no scratch: the caller falls back to the tiled kernel
-        plan.arrivals = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(args.partial) + per_cta * ctas);
+        if (ctas < 1) return false;    // no scratch: the caller falls back to the tiled kernel
+        plan.arrivals = args.ws_words;
     }
-    if (ctas < 1) return DSL_NOT_SERVED;
     plan.ctas = static_cast<int>(ctas);
     plan.cluster_runs = cluster_runs;
-    static std::atomic<unsigned long long> epoch_source{1};
-    plan.epoch = epoch_source.fetch_add(1) & 0xFFFFFFFFFFFFull;
-    if (plan.epoch == 0) plan.epoch = epoch_source.fetch_add(1) & 0xFFFFFFFFFFFFull;
+    return true;
+}
+
+template <int KIND, int TOK>
+static int launch_decode_one(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
+    using C = DecCfg<KIND, TOK>;
+    DecPlan plan;
+    size_t wanted = 0;
+    if (!plan_decode<KIND, TOK>(args, plan, &wanted)) return DSL_NOT_SERVED;
+    plan.epoch = next_epoch();
     CUtensorMap tw, tx;
     if (!make_tmap_u8(&tw, B, args.k_bytes, args.n, 0, STAGE_KB, 128)) return DSL_ERR_DRIVER;
     if (!make_tmap_u8(&tx, A, args.k_bytes, args.m_total, 0, STAGE_KB, TOK)) return DSL_ERR_DRIVER;
-    static bool attr_set = false;   // idempotent; a race here only repeats the same call
-    if (!attr_set) {
+    static PerDeviceInt attr_set;   // per device; idempotent, a race here only repeats the same call
+    const int dev = current_device_slot();
+    if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
+    if (attr_set.v[dev].load(std::memory_order_acquire) == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<KIND, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
-        attr_set = true;
+        attr_set.v[dev].store(1, std::memory_order_release);
     }
     // Programmatic stream serialisation: the grid may be set up (and, for a static weight, start its
     // weight stream) while the preceding kernel of the stream drains; griddep_wait() guards the rest.
@@ -616,15 +647,43 @@ static int launch_decode_one(const void* A, const void* B, const GemmArgs& args,
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 1;
-    if (cluster_runs > 1) {
+    if (plan.cluster_runs > 1) {
         attr[1].id = cudaLaunchAttributeClusterDimension;
-        attr[1].val.clusterDim.x = cluster_runs;
+        attr[1].val.clusterDim.x = plan.cluster_runs;
         attr[1].val.clusterDim.y = 1;
         attr[1].val.clusterDim.z = 1;
         cfg.numAttrs = 2;
     }
     cfg.attrs = attr;
     return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_decode_kernel<KIND, TOK>, tw, tx, args, plan));
+}
+
+template <int KIND>
+static bool plan_decode_kind(const GemmArgs& args, size_t* wanted) {
+    DecPlan plan;
+    if (args.m_total <= 16) return plan_decode<KIND, 16>(args, plan, wanted);
+    if (args.m_total <= 32) return plan_decode<KIND, 32>(args, plan, wanted);
+    if (args.m_total <= 64) return plan_decode<KIND, 64>(args, plan, wanted);
+    return plan_decode<KIND, 128>(args, plan, wanted);
+}
+
+static bool decode_domain(const GemmArgs& args) {
+    return args.group_offsets == nullptr && args.m_total <= DSL_DECODE_MAX_ROWS && args.act == DSL_ACT_NONE &&
+           args.out_sf == nullptr;
+}
+
+size_t decode_scratch_bytes(int kind, const GemmArgs& args, bool* served) {
+    size_t wanted = 0;
+    *served = false;
+    if (!decode_domain(args)) return 0;
+    switch (kind) {
+        case KIND_F8: *served = plan_decode_kind<KIND_F8>(args, &wanted); break;
+        case KIND_NVF4: *served = plan_decode_kind<KIND_NVF4>(args, &wanted); break;
+        case KIND_MXF4: *served = plan_decode_kind<KIND_MXF4>(args, &wanted); break;
+        case KIND_BF16: *served = plan_decode_kind<KIND_BF16>(args, &wanted); break;
+        default: break;
+    }
+    return *served ? wanted : 0;
 }
 
 template <int KIND>
@@ -638,9 +697,7 @@ static int launch_decode_kind(const void* A, const void* B, const GemmArgs& args
 
 // Returns DSL_NOT_SERVED when the problem is not one this kernel serves (the caller then uses the tiled kernels).
 int launch_gemm_decode(int kind, const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
-    if (args.group_offsets != nullptr || args.m_total > DSL_DECODE_MAX_ROWS || args.act != DSL_ACT_NONE ||
-        args.out_sf != nullptr)
-        return DSL_NOT_SERVED;
+    if (!decode_domain(args)) return DSL_NOT_SERVED;
     switch (kind) {
         case KIND_F8: return launch_decode_kind<KIND_F8>(A, B, args, st);
         case KIND_NVF4: return launch_decode_kind<KIND_NVF4>(A, B, args, st);

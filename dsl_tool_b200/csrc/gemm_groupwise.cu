@@ -224,32 +224,24 @@ gemm_fp8_groupwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     }
 }
 
-static int sm_count_gw() {
-    static int n = []() {
-        int dev = 0, v = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-        return v > 0 ? v : 148;
-    }();
-    return n;
-}
-
 template <bool SB_BLOCK, bool ACT>
 static int launch_gw(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
     CUtensorMap ta, tb;
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
     if (!make_tmap_u8(&ta, A, args.k_bytes, args.m_total, 0, STAGE_KB, BLOCK_M)) return DSL_ERR_DRIVER;
     if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, gw::BLOCK_N)) return DSL_ERR_DRIVER;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceInt attr_set;   // per device
+    const int dev = current_device_slot();
+    if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
+    if (attr_set.v[dev].load(std::memory_order_acquire) == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_kernel<SB_BLOCK, ACT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, gw::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
-        attr_set = true;
+        attr_set.v[dev].store(1, std::memory_order_release);
     }
     const long long m_tiles_max = (args.m_total + BLOCK_M - 1) / BLOCK_M + groups - 1;
     const long long max_tiles = m_tiles_max * ((args.n + gw::BLOCK_N - 1) / gw::BLOCK_N);
-    long long grid = max_tiles < sm_count_gw() ? max_tiles : sm_count_gw();
+    long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
     if (grid < 1) grid = 1;
     gemm_fp8_groupwise_kernel<SB_BLOCK, ACT><<<static_cast<unsigned>(grid), gw::THREADS, gw::SMEM_BYTES, st>>>(ta, tb, args);
     return static_cast<int>(cudaGetLastError());

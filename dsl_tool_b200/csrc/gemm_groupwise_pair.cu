@@ -234,14 +234,13 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     // Everything above touches no global memory, so under programmatic stream serialisation it runs while the
     // preceding kernel of the stream (the activation quantiser) drains; from here on that kernel's results are read.
     griddep_wait();
-    for (int g = threadIdx.x; g <= groups; g += blockDim.x)
-        s_offs[g] = args.group_offsets != nullptr ? args.group_offsets[g] : (g == 0 ? 0 : args.m_total);
+    load_group_offsets(s_offs, args.group_offsets, groups, args.m_total);
     __syncthreads();
     if (threadIdx.x == 0) {
         int t = 0;
         for (int g = 0; g < groups; ++g) {
             s_tile0[g] = t;
-            const int rows = s_offs[g + 1] - s_offs[g];
+            const int rows = monotone_rows(s_offs, g);
             if (rows > 0) t += (rows + TILE_M - 1) / TILE_M;
         }
         s_tile0[groups] = t;
@@ -388,14 +387,15 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     if (!make_tmap_u8(&ta, A, args.k_bytes, args.m_total, 0, STAGE_KB, 128)) return DSL_ERR_DRIVER;
     if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, 128)) return DSL_ERR_DRIVER;
     if (!make_tmap_u8(&tbn, B, args.k_bytes, args.n, groups, STAGE_KB, gwp::NARROW_N / 2)) return DSL_ERR_DRIVER;
-    static int max_clusters = 0;
+    static PerDeviceInt clusters_of;   // per kernel instantiation and device; idempotent set-up
+    const int dev = current_device_slot();
+    if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
+    int max_clusters = clusters_of.v[dev].load(std::memory_order_acquire);
     if (max_clusters == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, gwp::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int sms = sm_count();
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(sms > 1 ? (sms / 2) * 2 : 2));
         cfg.blockDim = dim3(gwp::THREADS);
@@ -404,6 +404,7 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
         e = cudaOccupancyMaxActiveClusters(&n, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>, &cfg);
         max_clusters = (e == cudaSuccess && n > 0) ? n : (sms > 1 ? sms / 2 : 1);
         (void)cudaGetLastError();
+        clusters_of.v[dev].store(max_clusters, std::memory_order_release);
     }
     const long long m_tiles_max = (args.m_total + gwp::TILE_M - 1) / gwp::TILE_M + groups - 1;
     const long long max_tiles = m_tiles_max * ((args.n + gwp::TILE_N - 1) / gwp::TILE_N);
@@ -433,15 +434,16 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
 int groupwise_pair_schedule_host(const int* group_offsets, int groups, int m_total, int n, int pairs, int band, int whole_tiles_only,
                                  int* out, int max_items) {
     using namespace gwp;
-    const int one[2] = {0, m_total};
-    const int* offs = group_offsets != nullptr ? group_offsets : one;
     if (group_offsets == nullptr) groups = 1;
-    int* tile0 = static_cast<int*>(malloc(sizeof(int) * (groups + 1)));
+    int* tile0 = static_cast<int*>(malloc(sizeof(int) * 2 * (groups + 1)));
     if (tile0 == nullptr) return -1;
+    int* offs = tile0 + (groups + 1);   // the kernel's own sanitised copy of the offsets
+    for (int g = 0; g <= groups; ++g)
+        offs[g] = group_offsets != nullptr ? clamp_offset(group_offsets[g], m_total) : (g == 0 ? 0 : m_total);
     int t = 0;
     for (int g = 0; g < groups; ++g) {
         tile0[g] = t;
-        const int rows = offs[g + 1] - offs[g];
+        const int rows = monotone_rows(offs, g);
         if (rows > 0) t += (rows + TILE_M - 1) / TILE_M;
     }
     tile0[groups] = t;

@@ -132,8 +132,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
     }
-    for (int g = threadIdx.x; g <= groups; g += blockDim.x)
-        s_offs[g] = args.group_offsets != nullptr ? args.group_offsets[g] : (g == 0 ? 0 : args.m_total);
+    load_group_offsets(s_offs, args.group_offsets, groups, args.m_total);
     if (C::SF_ATOMS > 0) {
         uint32_t* z = reinterpret_cast<uint32_t*>(smem + C::OFF_SFA);
         for (int i = threadIdx.x; i < C::NUM_STAGES * (C::SFA_STAGE + C::SFB_STAGE) / 4; i += blockDim.x) z[i] = 0u;
@@ -145,7 +144,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int g = 0; g < groups; ++g) {
             s_tile0[g] = t;
             s_sft0[g] = st;
-            const int rows = s_offs[g + 1] - s_offs[g];
+            const int rows = monotone_rows(s_offs, g);
             if (rows > 0) {
                 t += (rows + pr::TILE_M - 1) / pr::TILE_M;
                 st += (rows + 127) / 128;
@@ -384,13 +383,14 @@ static int launch_pair_one(const void* A, const void* B, const GemmArgs& args, l
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
     if (!make_tmap_u8(&ta, A, args.k_bytes, args.m_total, 0, STAGE_KB, 128)) return DSL_ERR_DRIVER;
     if (!make_tmap_u8(&tb, B, args.k_bytes, args.n, groups, STAGE_KB, 128)) return DSL_ERR_DRIVER;
-    static int max_clusters = 0;   // per kernel instantiation; idempotent set-up
+    static PerDeviceInt clusters_of;   // per kernel instantiation and device; idempotent set-up
+    const int dev = current_device_slot();
+    if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
+    int max_clusters = clusters_of.v[dev].load(std::memory_order_acquire);
     if (max_clusters == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int sms = sm_count();
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(sms > 1 ? (sms / 2) * 2 : 2));
         cfg.blockDim = dim3(192);
@@ -400,6 +400,7 @@ static int launch_pair_one(const void* A, const void* B, const GemmArgs& args, l
         max_clusters = (e == cudaSuccess && n > 0) ? n : (sms > 1 ? sms / 2 : 1);
         (void)cudaGetLastError();
         if (getenv("DSLGEMM_DEBUG") != nullptr) fprintf(stderr, "[dslgemm] pair kernel kind %d: %d resident clusters (occupancy query %s)\n", KIND, max_clusters, cudaGetErrorName(e));
+        clusters_of.v[dev].store(max_clusters, std::memory_order_release);
     }
     long long clusters = max_tiles < max_clusters ? max_tiles : max_clusters;
     if (clusters < 1) clusters = 1;

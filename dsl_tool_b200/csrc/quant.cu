@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 #include <float.h>
 
+#include "gemm_tiles.cuh"
 #include "ptx.cuh"
 #include "quant.cuh"
 
@@ -84,8 +85,11 @@ __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
 // (r = x - q*s exactly, by FMA; q' = RN(q + r*y)) brings it within half an ulp plus a sliver, and a
 // second one gives the correctly rounded quotient (Markstein's theorem: a faithful q and a correctly
 // rounded reciprocal suffice), i.e. the very value __fdiv_rn returns.  The residual is exact unless
-// it underflows, which needs |x| < 2^-125; the scale is at least 1e-12, so such a quotient is below
+// it underflows, which needs |x| < 2^-125; with a scale of at least 1e-12 such a quotient is below
 // 2^-85, far under the smallest E4M3 rounding boundary (2^-10), and converts to zero either way.
+// Scales the library derives are never smaller; a caller-given scale can be (its reciprocal may even
+// overflow), so quant16_e4m3 takes this path only for scales inside [1e-12, 3e38] and divides for
+// real otherwise.
 // Two values of q0 must pass through untouched: a zero (the zero residual is +0 and would turn -0
 // into +0) and an infinity (Inf - Inf poisons the residual); both are the fixed points of q -> 2q.
 // A NaN stays a NaN through the corrections.  Six FMA-pipe instructions, one compare and one select
@@ -98,7 +102,7 @@ __device__ __forceinline__ float div_for_e4m3(float x, float s, float inv) {
 }
 __device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
     uint32_t w[4];
-    if (s <= 3.0e38f) {
+    if (s >= 1e-12f && s <= 3.0e38f) {
         const float inv = __frcp_rn(s);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -106,7 +110,8 @@ __device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
             uint32_t hi = cvt_e4m3x2(div_for_e4m3(v[4 * i + 2], s, inv), div_for_e4m3(v[4 * i + 3], s, inv));
             w[i] = lo | (hi << 16);
         }
-    } else {   // an infinite scale (an Inf among the inputs): 0 * Inf would poison the residual; divide for real
+    } else {   // an infinite scale (an Inf among the inputs: 0 * Inf would poison the residual), or a given
+               // scale too small for the residual argument above (also zero, negative, NaN): divide for real
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             uint32_t lo = cvt_e4m3x2(__fdiv_rn(v[4 * i], s), __fdiv_rn(v[4 * i + 1], s));
@@ -296,13 +301,14 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict_
     sfi.offs = nullptr;
     sfi.tile0 = nullptr;
     if (group_offsets != nullptr) {
-        for (int g = threadIdx.x; g <= num_groups; g += blockDim.x) s_offs[g] = group_offsets[g];
+        // untrusted device data: sanitised exactly as the GEMM kernels do, so both derive the same scale tiles
+        load_group_offsets(s_offs, group_offsets, num_groups, static_cast<int>(M));
         __syncthreads();
         if (threadIdx.x == 0) {
             int t = 0;
             for (int g = 0; g < num_groups; ++g) {
                 s_tile0[g] = t;
-                t += (s_offs[g + 1] - s_offs[g] + 127) >> 7;
+                t += (monotone_rows(s_offs, g) + 127) >> 7;
             }
             s_tile0[num_groups] = t;
         }

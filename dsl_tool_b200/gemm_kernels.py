@@ -91,7 +91,9 @@ def _make_output(dev, M: int, nc: int, out_dtype, out_global_scale: Scalar, offs
 
 def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
               row_scale: Optional[torch.Tensor], col_scale: Optional[torch.Tensor], keep: list,
-              b_static: bool = False, activation: Optional[str] = None) -> _lib.Epilogue:
+              b_static: bool = False, activation: Optional[str] = None, problem: Optional[tuple] = None) -> _lib.Epilogue:
+    """`problem` = (DSL_OP_* code, M, N, K, groups): the scratch the kernels can use for it is asked
+    from the library (dsl_workspace_bytes) and attached; without it no scratch is passed."""
     ep = _lib.Epilogue()
     ep.b_is_static = 1 if b_static else 0
     ep.activation = _activation_code(activation)
@@ -113,9 +115,12 @@ def _epilogue(dev, scale_a: Scalar, scale_b: Scalar, out: torch.dtype,
             keep.append(t)
             setattr(ep, name, t.data_ptr())
     ep.out_dtype = _lib.F32 if out in (None, torch.float32) else _lib.BF16
-    ws = _lib.workspace(dev)
-    ep.workspace = ws.data_ptr()
-    ep.workspace_bytes = ws.numel()
+    if problem is not None:
+        with torch.cuda.device(dev):
+            ws = _lib.workspace(dev, int(_lib.lib().dsl_workspace_bytes(*problem)))
+        if ws is not None:
+            ep.workspace = ws.data_ptr()
+            ep.workspace_bytes = ws.numel()
     return ep
 
 
@@ -155,7 +160,8 @@ def gemm_fp8_quantized(qa: torch.Tensor, qb_nk: torch.Tensor, scale_a: Scalar, s
         raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major bytes, got {tuple(qb_nk.shape)}")
     nc = _out_cols(n, activation)
     keep: list = []
-    ep = _epilogue(dev, scale_a, scale_b, None, row_scale, col_scale, keep, b_static, activation)
+    ep = _epilogue(dev, scale_a, scale_b, None, row_scale, col_scale, keep, b_static, activation,
+                   (_lib.OP_GEMM_FP8, M, n, K, groups))
     out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_fp8(qa.data_ptr(), qb_nk.data_ptr(), out.data_ptr(), ldc, M, n, K, _lib.ptr(offs),
@@ -225,7 +231,8 @@ def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor,
         raise ValueError("scale buffers are smaller than the tiled layout needs")
     nc = _out_cols(n, activation)
     keep: list = []
-    ep = _epilogue(dev, global_scale_a, global_scale_b, None, row_scale, col_scale, keep, b_static, activation)
+    ep = _epilogue(dev, global_scale_a, global_scale_b, None, row_scale, col_scale, keep, b_static, activation,
+                   (_lib.OP_GEMM_FP4_NV if fmt == _lib.FP4_NV else _lib.OP_GEMM_FP4_MX, M, n, K, groups))
     out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_fp4(pa.data_ptr(), pb_nk.data_ptr(), _bytes2d(sfa).data_ptr(),
@@ -247,7 +254,7 @@ def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torc
         raise ValueError(f"weight must be [{groups}*{n}, {K}] K-major, got {tuple(b_nk.shape)}")
     nc = _out_cols(n, activation)
     keep: list = []
-    ep = _epilogue(dev, scale_a, scale_b, None, None, None, keep, False, activation)
+    ep = _epilogue(dev, scale_a, scale_b, None, None, None, keep, False, activation, (_lib.OP_GEMM_BF16, M, n, K, groups))
     out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_gemm_bf16(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), ldc, M, n, K, _lib.ptr(offs),

@@ -100,8 +100,11 @@ typedef struct {
     const float* row_scale;     /* [M_total] or NULL: per-token rescale */
     const float* col_scale;     /* [G, N]   or NULL: per-channel rescale */
     int out_dtype;              /* DSL_F32 or DSL_BF16 */
-    void* workspace;            /* optional scratch (16-byte aligned) for split-K partial sums, or NULL */
-    size_t workspace_bytes;     /* its size; decode shapes (few rows, long K) use up to 8*M*N*4 bytes */
+    void* workspace;            /* optional scratch (16-byte aligned) for partial sums along K, or NULL */
+    size_t workspace_bytes;     /* its size: dsl_workspace_bytes() says what a problem can put to use (less is
+                                   allowed and only slower).  The first 64 KiB are a header in which only the
+                                   weight-streaming kernel's arrival words ever live; the buffer need not be cleared,
+                                   and launches that may overlap on the GPU need separate buffers */
     int b_is_static;            /* non-zero: B and its scale bytes were complete before the kernel that precedes
                                    this call in the stream was launched (a pre-packed weight).  The weight-streaming
                                    kernel is launched with programmatic stream serialisation and then starts
@@ -124,6 +127,17 @@ typedef struct {
     float out_gs_host;          /* global scale of the quantised result ... */
     const float* out_gs_dev;    /* ... overridden by this device scalar when non-NULL */
 } dsl_epilogue;
+
+/*
+ * Bytes of dsl_epilogue.workspace that the GEMM entry point `op` can put to use for a dense M x N x K
+ * problem on the CURRENT device (it asks for the device's SM count), header included; 0 when the kernels
+ * that serve the problem need no scratch (large M, row groups, decode shapes whose partial tiles are
+ * combined inside thread-block clusters, the group-scaled FP8 GEMM).  Decode shapes with more 128-column
+ * tiles than SMs take 2 partial tiles of TOK x 128 floats per CTA (TOK = 16 or 32 tokens); other
+ * problems that would leave more than half of the SMs idle take up to 8 K-slices of M x N floats.
+ */
+enum { DSL_OP_GEMM_FP8 = 0, DSL_OP_GEMM_BF16 = 1, DSL_OP_GEMM_FP4_NV = 2, DSL_OP_GEMM_FP4_MX = 3, DSL_OP_GEMM_FP8_GROUPWISE = 4 };
+size_t dsl_workspace_bytes(int op, long long M, int N, int K, int groups);
 
 /*
  * Dense / grouped FP8 E4M3 GEMM, per-tensor scales: C[m,n] = sum_k A[m,k] B[n,k] * scale_a * scale_b.
@@ -210,20 +224,30 @@ int dsl_moe_combine(const void* y, int y_dtype, const int* ids, const int* dest,
 
 /*
  * dsl_gemm_fp4 for callers that cannot allocate device memory (no counterpart in the
- * reference).  Same operands and result as dsl_gemm_fp4 on a dense problem, but the split-K
- * scratch is a fixed DSL_STATIC_SCRATCH_BYTES array inside the library instead of
+ * reference).  Same operands and result as dsl_gemm_fp4 on a dense problem, but the scratch for
+ * partial sums along K is a fixed DSL_STATIC_SCRATCH_BYTES array inside the library instead of
  * ep->workspace (which is ignored), so nothing but inputs and outputs is passed and the call
- * performs no allocation.  Meant for decode-sized problems: it returns DSL_ERR_TOO_LARGE unless
- * 2 * M * N * 4 bytes fit in the array.  The first call on each device looks up the array's
- * device address (cudaGetSymbolAddress); make that call before any stream capture.  All calls
- * share the one array and it keeps the previous call's contents; every element a call reads
- * has been written by that call first, so nothing needs clearing, but two calls that overlap
- * on the GPU (different streams) race on it.
+ * performs no allocation.  Meant for decode-sized problems: it returns DSL_ERR_TOO_LARGE when
+ * dsl_workspace_bytes() for the problem exceeds the array (e.g. 32 tokens against more than
+ * 126 x 128 columns on a 148-SM part); problems that need no scratch at all pass through.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ * make that call before any stream capture.  All calls share the one array and it keeps the
+ * previous call's contents.  Partial sums are always written by a call before that call reads
+ * them.  The arrival words in the array's first 64 KiB are the exception: they are read first,
+ * and are safe because the array starts zeroed, nothing but those words is ever stored there,
+ * each launch tags its words with an epoch of its own and the kernel zeroes a word once its
+ * tile is finished.  So nothing needs clearing between calls, but two calls that overlap on
+ * the GPU (different streams) race on the array.
  */
 #define DSL_STATIC_SCRATCH_BYTES (4u << 20)
 int dsl_gemm_fp4_static_scratch(const uint8_t* A, const uint8_t* B, const uint8_t* sfa, const uint8_t* sfb,
                                 int format, void* C, long long ldc, long long M, int N, int K,
                                 const dsl_epilogue* ep, uint32_t* status, void* stream);
+
+/* Test hook for the entry point above: copies `bytes` bytes between the static array (from `offset`) and the
+ * device buffer `user`, into the array when to_array != 0, ordered on `stream`.  Lets a test put foreign
+ * bytes into the array before a call and see afterwards what the call wrote.  Not for production use. */
+int dsl_selftest_static_scratch_copy(void* user, size_t offset, size_t bytes, int to_array, void* stream);
 
 /* Runs one bounded wait on a barrier nothing ever signals and reports DSL_ST_TIMEOUT_TEST
  * in *status after about `limit_us` microseconds: exercises the give-up path without
@@ -232,7 +256,9 @@ int dsl_selftest_bounded_wait(uint32_t* status, unsigned limit_us, void* stream)
 
 /* The work list of the group-scaled FP8 CTA-pair kernel for a problem, computed on the HOST by the kernel's own
  * scheduler code (no CUDA call, no GPU needed): for tests that every output element is covered exactly once.
- * group_offsets: HOST int32 [num_groups + 1] row offsets, or NULL for one dense group of m_total rows.  pairs = CTA
+ * group_offsets: HOST int32 [num_groups + 1] row offsets, or NULL for one dense group of m_total rows; they pass through
+ * the kernel's own sanitiser (entries clamped to [0, m_total] and raised to their predecessor), so malformed offsets
+ * are accepted here and the items show what the kernel would do with them.  pairs = CTA
  * pairs of the launch (74 on a 148-SM part), band <= 0 = the default raster band, whole_tiles_only = 1 switches the
  * cutting of the last round off.  Item i (it runs on pair i % pairs, in order) is written to out[6 i ..] as
  * {pair, group, row0, row_end, n0, width}: rows [row0, min(row0 + 256, row_end)) x columns [n0, min(n0 + width, N)).

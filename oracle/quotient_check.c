@@ -11,7 +11,13 @@
  * below 2^-11 are only required to stay below the smallest E4M3 rounding boundary, 2^-10 (there the residual may
  * underflow and both values convert to zero).
  *
- * usage: quotient_check <scales> <mode>    mode 0: every bf16 dividend up to amax; mode 1: random fp32 dividends
+ * A caller may also GIVE the scale (dsl_quant_fp8 with scale_given): then it can be far below 1e-12, its
+ * reciprocal can overflow and the residual argument no longer holds, so the quantiser uses the corrected
+ * quotient only for scales inside [1e-12, 3e38] and a real division otherwise.  Mode 2 checks that rule over
+ * scales drawn from the whole fp32 range (subnormals included) against dividends of any magnitude.
+ *
+ * usage: quotient_check <scales> <mode>    mode 0: every bf16 dividend up to amax; mode 1: random fp32 dividends;
+ *                                          mode 2: given scales of any size, random dividends
  * prints "checked N mismatches M" and exits 0 when M == 0.
  */
 #include <math.h>
@@ -31,6 +37,12 @@ static float quotient(float x, float s, float y) {
     return (q0 + q0 == q0) ? q0 : q2;
 }
 
+/* what quant16_e4m3 computes for one element */
+static float quotient_guarded(float x, float s) {
+    if (s >= 1e-12f && s <= 3.0e38f) return quotient(x, s, 1.0f / s);
+    return x / s;
+}
+
 static long checked = 0, bad = 0;
 static void check(float x, float s, float y) {
     const float want = x / s;
@@ -46,6 +58,25 @@ static void check(float x, float s, float y) {
 int main(int argc, char** argv) {
     const long scales = argc > 1 ? atol(argv[1]) : 200;
     const int mode = argc > 2 ? atoi(argv[2]) : 0;
+    if (mode == 2) {
+        for (long it = 0; it < scales; ++it) {
+            const float s = from_bits((uint32_t)(rnd() % 0x7F800000u));        /* +0 ... just below +Inf */
+            for (int j = 0; j < 2048; ++j) {
+                /* dividends around the scale (quotients of E4M3 size) and anywhere else */
+                const uint32_t sb = (uint32_t)(rnd() % 0x7F800000u);
+                const float x = (j & 1) ? from_bits(sb) : s * (float)((double)(rnd() % 100000) / 128.0);
+                const float want = x / s, got = quotient_guarded(x, s);
+                if (fabsf(want) < 0x1p-11f) {
+                    if (!(fabsf(got) < 0x1p-10f)) ++bad;
+                } else if (memcmp(&got, &want, 4) != 0 && !(isnan(got) && isnan(want))) {
+                    ++bad;
+                }
+                ++checked;
+            }
+        }
+        printf("checked %ld mismatches %ld\n", checked, bad);
+        return bad == 0 ? 0 : 1;
+    }
     for (long it = 0; it < scales; ++it) {
         uint32_t ab = (uint32_t)(rnd() % 0x7F000000u);
         if (mode == 0 && (it & 1)) ab &= 0xFFFF0000u;      /* a bf16 amax every other time */

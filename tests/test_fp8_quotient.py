@@ -1,6 +1,7 @@
 """The E4M3 quantisers divide without a division: reciprocal of the scale + two FMA corrections.  This CPU check
 compiles oracle/quotient_check.c (the same arithmetic with libm's fmaf) and compares it with the IEEE quotient over
-every bf16 dividend for hundreds of scales and over millions of random fp32 dividends."""
+every bf16 dividend for hundreds of scales, over millions of random fp32 dividends, and - for scales a caller
+gives, which may be tiny - over the rule that sends scales outside [1e-12, 3e38] to a real division."""
 import os
 import subprocess
 
@@ -18,7 +19,7 @@ def checker(tmp_path_factory):
     return str(exe)
 
 
-@pytest.mark.parametrize("scales,mode", [(600, 0), (4000, 1)])
+@pytest.mark.parametrize("scales,mode", [(600, 0), (4000, 1), (2000, 2)])
 def test_fma_corrected_quotient_equals_division(checker, scales, mode):
     out = subprocess.run([checker, str(scales), str(mode)], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr

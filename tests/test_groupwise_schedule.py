@@ -90,4 +90,27 @@ def test_argument_errors():
     assert lib.dsl_selftest_groupwise_schedule(None, 1, 4096, 14336, 0, 0, 0, po, 4) == -2
     assert lib.dsl_selftest_groupwise_schedule(None, 1, 4096, 14336, 74, 0, 0, po, 4) == -6                # too many items
     bad = np.array([0, 10, 5], np.int32)
-    assert lib.dsl_selftest_groupwise_schedule(bad.ctypes.data_as(ctypes.c_void_p), 2, 5, 256, 74, 0, 0, po, 4) == -2
+    assert lib.dsl_selftest_groupwise_schedule(bad.ctypes.data_as(ctypes.c_void_p), 0, 5, 256, 74, 0, 0, po, 4) == -2
+
+
+@pytest.mark.parametrize("offs,m_total", [
+    ([0, 300, 5000], 600),            # last entry beyond the rows there are
+    ([0, 400, 100, 600], 600),        # decreasing
+    ([-50, 200, 10_000_000], 512),    # negative first entry, absurd last one
+    ([700, 650, 640], 600),           # everything out of range
+    ([0, 2_000_000_000, -2_000_000_000, 300], 300),
+])
+def test_malformed_offsets_stay_inside_the_operands(offs, m_total):
+    """Row-group offsets are device data the kernel cannot refuse; its sanitiser (entries clamped to [0, m_total],
+    each raised to its predecessor) must keep every item's rows inside [0, m_total) and never cover a row twice."""
+    n = 512
+    items = _schedule(np.array(offs, np.int32), m_total, n, 7)
+    hits = np.zeros(m_total, np.int32)
+    for pair, group, row0, row_end, n0, width in items:
+        assert 0 <= row0 < row_end <= m_total
+        if n0 == 0:
+            hits[row0:min(row0 + 256, row_end)] += 1
+    assert hits.max(initial=0) <= 1
+    # the sanitised table: clamp, then running maximum
+    clean = np.maximum.accumulate(np.clip(np.array(offs, np.int64), 0, m_total))
+    assert hits.sum() == clean[-1] - clean[0]
