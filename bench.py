@@ -1,22 +1,34 @@
 """Benchmark of the quantised-GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+                    [--scaling strong|weak] [--no-sweep] [--min-seconds S] [--graph]
 
 One "step" = one pass of the hot path over one batch of synthetic input: quantise / scale-pack
-the activations (one kernel) and run the GEMM against weights that were quantised once.  The
-default workload is the FP8 groupwise GEMM at the Llama-3-8B MLP shape (M=4096, K=4096,
-N=14336; 1x128 activation scales, 128x128 weight-block scales, bf16 output).  Inputs are
-seeded synthetic tensors of the stated shapes and distributions.
+the activations and run the GEMM against weights that were quantised once, through the library's
+public callable (`linear`).  The default workload is the FP8 groupwise GEMM at the Llama-3-8B MLP
+shape (M=4096, K=4096, N=14336; 1x128 activation scales, 128x128 weight-block scales, bf16
+output).  Inputs are seeded synthetic tensors of the stated shapes and distributions.
 
-Prints ONE JSON line (rank 0).  `value` is aggregate TFLOP/s over all ranks with inputs
-resident in HBM; `e2e` is the same metric through the public callable with activations in
-pinned host memory (host->device copy of the activations and device->host copy of the result
-inside the timed region).  With N > 1 each rank holds its own column shard of the weight
-(dense) or its own experts (MoE) of the same per-rank size, no data-path collective.
+Prints ONE JSON line (rank 0).
+  * `value`: aggregate TFLOP/s over all ranks with inputs resident in HBM.  K steps are timed between
+    two barriers with CUDA events, and that K-step block is repeated until the timed region lasts at
+    least `--min-seconds` (default 1 s), so that the figure is taken at the clocks the part sustains;
+    `ms_per_step` is the median block, `burst` the first one.
+  * `roofline`: the GEMM kernel alone, from its own pair of events in a K-step pass that follows the
+    timed blocks without a pause.
+  * `e2e`: the same metric through the public callable with the activations in pinned host memory
+    (host->device copy of the activations and device->host copy of the result inside the timed region).
+  * `sweep`: one short record per further configuration (decode shapes replayed as CUDA graphs).
+  * `cpu_baseline`: the reference's own CPU emulation (a copy made by `make -C oracle ref_py`) on a
+    bounded slab of the workload, the numpy restatement beside it.
+With N > 1 the ONE problem is split across the ranks (`--scaling strong`, the default): 128-aligned
+column ranges of the weight for the dense GEMMs, contiguous expert ranges for the MoE GEMMs, no
+data-path collective.  `--scaling weak` gives every rank a full-size shard instead.
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
 import os
 import statistics
@@ -32,7 +44,6 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (kind, M, K, N, act std/outliers, weight std, description)
     "fp8_groupwise_llama8b_mlp": dict(kind="fp8_block128", M=4096, K=4096, N=14336, wstd=0.02, outliers=False),
     "fp8_groupwise_m1024": dict(kind="fp8_block128", M=1024, K=4096, N=14336, wstd=0.02, outliers=False),
     "fp8_per_tensor_1024": dict(kind="fp8", M=1024, K=1024, N=1024, wstd=1.0, outliers=False),
@@ -44,14 +55,18 @@ WORKLOADS = {
     "nvfp4_m1": dict(kind="nvfp4", M=1, K=8192, N=8192, wstd=0.02, outliers=True),
     "mxfp4_llama70b_up": dict(kind="mxfp4", M=8192, K=8192, N=28672, wstd=0.015, outliers=False),
     "mxfp4_llama70b_down": dict(kind="mxfp4", M=8192, K=28672, N=8192, wstd=0.015, outliers=False),
+    # the up projection with the full result wanted on every rank: one NCCL all-gather of the column shards per step
+    "mxfp4_llama70b_up_gather": dict(kind="mxfp4", M=8192, K=8192, N=28672, wstd=0.015, outliers=False, gather=True),
     "moe_nvfp4": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
+    # the same layer under skewed routing: per-expert logit bias N(0, 0.6), one expert nobody is routed to
+    "moe_nvfp4_skewed": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02, skew=0.6),
     "moe_fp8_groupwise": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
     "moe_nvfp4_swiglu": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02, act="swiglu"),
     "moe_nvfp4_swiglu_nvfp4out": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
                                       act="swiglu", out="nvfp4"),
     "moe_fp8_groupwise_swiglu": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
                                      act="swiglu"),
-    # config C5 fed the way a layer feeds it: 16384 token rows + their routing; the tokens are quantised ONCE and the
+    # the MoE GEMM fed the way a layer feeds it: 16384 token rows + their routing; the tokens are quantised ONCE and the
     # packed rows dispatched to expert-sorted order (step = plan + quantise + dispatch + grouped GEMM)
     "moe_nvfp4_tokens": dict(kind="nvfp4", tokens_in=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
     # the whole MoE feed-forward layer around the two grouped GEMMs (router, plan, quantise once, dispatch,
@@ -60,27 +75,37 @@ WORKLOADS = {
                             hidden_gs=0.01),
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
 }
+DEFAULT_WORKLOAD = "fp8_groupwise_llama8b_mlp"
+# further configurations reported in `sweep` (one GPU) ...
+SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_m1", "nvfp4_m16", "nvfp4_m128", "nvfp4_m1024",
+              "mxfp4_llama70b_up", "mxfp4_llama70b_down", "moe_nvfp4", "moe_nvfp4_tokens", "moe_nvfp4_skewed",
+              "moe_fp8_groupwise", "moe_layer_nvfp4"]
+# ... and the sharded ones when the problem is split over several GPUs
+SWEEP_SHARDED = ["mxfp4_llama70b_up", "mxfp4_llama70b_up_gather", "mxfp4_llama70b_down", "moe_nvfp4", "moe_fp8_groupwise",
+                 "moe_layer_nvfp4"]
 DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
-# dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from an ncu capture of the
-# full-size workload (profiles/): bytes.  None where no capture exists.
+# dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from ncu captures of the
+# full-size workloads: bytes.  None where no capture exists.
 NCU_TRAFFIC = {"fp8_groupwise_llama8b_mlp": 77.1e6 + 74.9e6,
                "nvfp4_8192": 164.5e6 + 105.9e6,
                "nvfp4_m16": 37.93e6 + 0.28e6}      # decode: GEMM + quantiser launch (whole step)
 PEAK_MULT = {"fp8": 2.0, "fp8_block128": 2.0, "nvfp4": 4.0, "mxfp4": 4.0, "bf16": 1.0}
+STATED_PEAK = {"fp8": 4500.0, "fp8_block128": 4500.0, "nvfp4": 9000.0, "mxfp4": 9000.0, "bf16": 2250.0}   # dense TFLOP/s
+STATED_HBM = 8000.0                                                                                      # GB/s
 
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return p["bf16_tflops"], p["hbm_gbs"], "measured"
-    return 1590.0, 6650.0, "fallback"
+        return p["bf16_tflops"], p.get("bf16_tflops_sustained"), p["hbm_gbs"], "measured"
+    return 1590.0, 1400.0, 6650.0, "fallback"
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks, power and throttle reasons while a timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw")
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
@@ -93,34 +118,66 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def mark(self) -> int:
+        return len(self.rows)
+
+    def summary(self, first: int = 0, last=None):
+        rows = self.rows[first:last]
+        num = lambda s: s.replace(".", "", 1).isdigit()
+        sm = [float(r[0]) for r in rows if len(r) >= 7 and num(r[0])]
+        mx = [float(r[1]) for r in rows if len(r) >= 7 and num(r[1])]
+        pw = [float(r[6]) for r in rows if len(r) >= 7 and num(r[6])]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[2 + i] == "Active" for r in rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm), "power_w_max": max(pw) if pw else None}
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        return self.summary()
 
 
-def make_moe_offsets(rng, tokens, experts, topk):
+def make_moe_offsets(rng, tokens, experts, topk, skew=0.0):
     logits = rng.standard_normal((tokens, experts)).astype(np.float32)
+    if skew > 0:
+        bias = (rng.standard_normal(experts) * skew).astype(np.float32)
+        bias[5 % experts] = -1e9                      # an expert without rows
+        logits += bias[None, :]
     top = np.argpartition(-logits, topk - 1, axis=1)[:, :topk]
     counts = np.bincount(top.reshape(-1), minlength=experts)
     return np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
 
 
+def workload_config(name, scaling, sets):
+    """The `config` object of the JSON line: identical in both arms (--impl ours / reference)."""
+    cfg = WORKLOADS[name]
+    out = {"workload": name, "format": cfg["kind"]}
+    if cfg.get("moe") or cfg.get("tokens_in") or cfg.get("layer"):
+        out.update(M=cfg["tokens"] * cfg["topk"], K=cfg["K"], N=cfg.get("N", 2 * cfg.get("H", 0)), experts=cfg["experts"],
+                   tokens=cfg["tokens"], topk=cfg["topk"], moe=True)
+    else:
+        out.update(M=cfg["M"], K=cfg["K"], N=cfg["N"], moe=False)
+    out["out"] = ("NVFP4 [M, N/2] = quantise(silu(gate) * up), both folded in the GEMM epilogue" if cfg.get("out") == "nvfp4"
+                  else "bf16 [M, N/2] = silu(gate) * up, folded in the GEMM epilogue" if cfg.get("act") else "bf16")
+    out["step"] = "activation quantise + GEMM, weights quantised once"
+    out["scaling"] = ("one problem split across the ranks (column ranges / expert ranges), no collective" if scaling == "strong"
+                      else "every rank holds a full-size shard, no collective")
+    out["l2"] = f"inputs rotate over {sets} sets (larger than the 126 MB L2)"
+    return out
+
+
 def build_workload(name, rank, world, device, sets, strong=False):
-    """Returns dict(step=callable(i)->out, gemm=callable, flops, rows, desc...) with `sets`
-    rotating copies of inputs so consecutive steps never reuse L2-resident operands."""
+    """Returns dict(step=callable(i)->out, ...) with `sets` rotating copies of the inputs so that
+    consecutive steps never reuse L2-resident operands."""
     from dsl_tool_b200 import pack_weight
     from dsl_tool_b200.gemm_kernels import linear
     cfg = WORKLOADS[name]
@@ -135,13 +192,13 @@ def build_workload(name, rank, world, device, sets, strong=False):
         experts = cfg["experts"]          # weak scaling keeps 64 local experts (and their routed rows) per GPU
         if strong:                        # strong scaling: one global routing, this rank owns experts/world of them
             from dsl_tool_b200.sharding import expert_ranges, local_rows
-            glob = make_moe_offsets(np.random.default_rng(99), cfg["tokens"], experts, cfg["topk"])
+            glob = make_moe_offsets(np.random.default_rng(99), cfg["tokens"], experts, cfg["topk"], cfg.get("skew", 0.0))
             first, last = expert_ranges(experts, world)[rank]
             _, _, loc = local_rows(glob, first, last)
             offs_np = np.asarray(loc, dtype=np.int32)
             experts = last - first
         else:
-            offs_np = make_moe_offsets(np.random.default_rng(99 + rank), cfg["tokens"], experts, cfg["topk"])
+            offs_np = make_moe_offsets(np.random.default_rng(99 + rank), cfg["tokens"], experts, cfg["topk"], cfg.get("skew", 0.0))
         offs = torch.from_numpy(offs_np).to(device)
         M, K, N = int(offs_np[-1]), cfg["K"], cfg["N"]
         wshape = (experts, N, K)
@@ -154,10 +211,12 @@ def build_workload(name, rank, world, device, sets, strong=False):
         wshape = (1, N, K)
     acts, wts = [], []
     for s in range(sets):
-        a = torch.randn((M, K), generator=g, device=device, dtype=torch.float32)
+        # strong scaling: the activations of the one problem are the same on every rank
+        ga = torch.Generator(device=device).manual_seed(4321 + s) if (strong and not cfg.get("moe")) else g
+        a = torch.randn((M, K), generator=ga, device=device, dtype=torch.float32)
         if cfg.get("outliers"):
-            mask = torch.rand((M, K), generator=g, device=device) < 1e-3
-            sign = torch.where(torch.rand((M, K), generator=g, device=device) < 0.5, -20.0, 20.0)
+            mask = torch.rand((M, K), generator=ga, device=device) < 1e-3
+            sign = torch.where(torch.rand((M, K), generator=ga, device=device) < 0.5, -20.0, 20.0)
             a = torch.where(mask, sign, a)
         acts.append(a.to(torch.bfloat16))
         del a
@@ -165,8 +224,14 @@ def build_workload(name, rank, world, device, sets, strong=False):
         wts.append(pack_weight(w, kind, layout="nk", gate_up_interleave=cfg.get("act") == "swiglu"))
         del w
     torch.cuda.synchronize()
+    gather_ranges = None
+    if cfg.get("gather") and strong and world > 1:
+        from dsl_tool_b200.sharding import all_gather_columns, column_ranges
+        gather_ranges = column_ranges(cfg["N"], world)
 
     def step(i, a=None):
+        if gather_ranges is not None:
+            return all_gather_columns(linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype=torch.bfloat16), gather_ranges)
         if cfg.get("out") == "nvfp4":    # result quantised in the epilogue with a fixed (calibrated) global scale
             return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype="nvfp4", out_global_scale=1.0 / 2688.0,
                           expert_offsets=offs, activation=cfg.get("act"))[0]
@@ -179,7 +244,7 @@ def build_workload(name, rank, world, device, sets, strong=False):
 
 def build_layer_workload(cfg, rank, world, device, sets, strong, g):
     """Whole MoE layer.  Weak scaling: every rank owns a full set of experts and its own tokens; strong
-    scaling: the experts of one layer are split over the ranks, tokens replicated, partial results all-reduced."""
+    scaling: the experts of one layer are split over the ranks, tokens replicated, partial results reduce-scattered."""
     from dsl_tool_b200 import MoEWeights, moe_forward
     T, E, k, K, H, D = cfg["tokens"], cfg["experts"], cfg["topk"], cfg["K"], cfg["H"], cfg["D"]
     acts, logits, wts = [], [], []
@@ -276,44 +341,106 @@ def split_step(wl):
     return quant, gemm
 
 
-def cpu_baseline(name, sample_rows, steps=1, warmup=0):
-    """The oracle's fp32-accumulated dequantised GEMM (numpy, all host threads) on the first
-    `sample_rows` activation rows of the workload, full N and K.  Returns (TFLOP/s, cores, text)."""
+# ------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own emulation where a copy of it was built, the numpy restatement otherwise
+# ------------------------------------------------------------------------------------------------
+
+def reference_emulation():
+    """The reference's CPU-runnable tiled GEMMs (`fp8_gemm_tiled`, `grouped_gemm_tiled`), loaded from the copy
+    that `make -C oracle ref_py REFERENCE_ROOT=...` places under oracle/_ref/ (never from the package)."""
+    path = os.path.join(ROOT, "oracle", "_ref", "tilelang_gemm_kernels.py")
+    if not os.path.exists(path):
+        return None
+    import contextlib
+    import io
+    spec = importlib.util.spec_from_file_location("reference_tilelang_gemm_kernels", path)
+    mod = importlib.util.module_from_spec(spec)
+    with contextlib.redirect_stdout(io.StringIO()):      # it prints "TileLang not installed" on import
+        spec.loader.exec_module(mod)
+    return mod
+
+
+def cpu_operands(name, rows):
+    """Seeded operands of the workload, quantised by the oracle: (dequantised A [rows, K], dequantised B [N, K],
+    closure computing the oracle's product).  MoE workloads: one expert's rows against that expert's weight."""
     from oracle import quant_oracle as O
     cfg = WORKLOADS[name]
     kind = cfg["kind"]
     rng = np.random.default_rng(5)
-    K, N = cfg["K"], cfg["N"]
-    R = sample_rows
-    a = rng.standard_normal((R, K)).astype(np.float32)
+    K, N = cfg["K"], cfg.get("N", 2 * cfg.get("H", 0))
+    a = rng.standard_normal((rows, K)).astype(np.float32)
     w = (rng.standard_normal((N, K)) * cfg["wstd"]).astype(np.float32)
     if kind == "fp8_block128":
         qa, sa = O.quant_fp8_groupwise(a)
         qb, sbb = O.quant_fp8_block(w)
         sb = O.expand_block_scale(sbb, N)
-        fn = lambda: O.gemm_fp8_groupwise(qa, qb, sa, sb)
+        A = O.e4m3_decode(qa) * np.repeat(sa, 128, axis=1)[:, :K]
+        B = O.e4m3_decode(qb) * np.repeat(sb.T, 128, axis=1)[:, :K]
+        port = lambda: O.gemm_fp8_groupwise(qa, qb, sa, sb)
     elif kind == "fp8":
         qa, sa = O.quant_fp8_per_tensor(a)
         qb, sb = O.quant_fp8_per_tensor(w)
-        fn = lambda: O.gemm_fp8_per_tensor(qa, qb, sa, sb)
+        A, B = O.e4m3_decode(qa) * sa, O.e4m3_decode(qb) * sb
+        port = lambda: O.gemm_fp8_per_tensor(qa, qb, sa, sb)
     elif kind == "nvfp4":
         pa, sfa, gsa = O.quant_nvfp4(a)
         pb, sfb, gsb = O.quant_nvfp4(w)
-        fn = lambda: O.gemm_nvfp4(pa, sfa, gsa, pb, sfb, gsb)
+        A = O.dequant_fp4_values(pa, O.e4m3_decode(sfa), 16) * gsa
+        B = O.dequant_fp4_values(pb, O.e4m3_decode(sfb), 16) * gsb
+        port = lambda: O.gemm_nvfp4(pa, sfa, gsa, pb, sfb, gsb)
     elif kind == "mxfp4":
         pa, sfa = O.quant_mxfp4(a)
         pb, sfb = O.quant_mxfp4(w)
-        fn = lambda: O.gemm_mxfp4(pa, sfa, pb, sfb)
+        A = O.dequant_fp4_values(pa, O.e8m0_decode(sfa), 32)
+        B = O.dequant_fp4_values(pb, O.e8m0_decode(sfb), 32)
+        port = lambda: O.gemm_mxfp4(pa, sfa, pb, sfb)
     else:
-        fn = lambda: a @ w.T
-    for _ in range(warmup):
-        fn()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        fn()
-    dt = (time.perf_counter() - t0) / steps
+        A, B = a, w
+        port = lambda: a @ w.T
+    return A.astype(np.float32), B.astype(np.float32), port
+
+
+def cpu_arm(name, steps=1, warmup=0, rows_reference=64, rows_port=512, want_port=True):
+    """Times the CPU arm on a bounded slab of the workload (the first rows of A against the full weight).
+    Returns the `cpu_baseline` object.  kind "reference": the reference's own `fp8_gemm_tiled` (Python tile loops
+    of 64 x 64 x 32 over torch CPU matmuls, all host threads) fed the oracle's dequantised operands - it is
+    format-agnostic (`tile.float() @ tile.float()`); kind "port": the oracle's numpy dequantise + fp32 GEMM."""
+    cfg = WORKLOADS[name]
+    K, N = cfg["K"], cfg.get("N", 2 * cfg.get("H", 0))
     cores = os.cpu_count() or 1
-    return 2.0 * R * N * K / dt / 1e12, cores, dt, f"first {R} activation rows x full N={N}, K={K} (dequantise + fp32 GEMM per step)"
+    torch.set_num_threads(cores)
+    ref = reference_emulation()
+    out = {"unit": "TFLOP/s", "cores": cores}
+    if ref is not None:
+        R = rows_reference
+        A, B, _ = cpu_operands(name, R)
+        At, Bt = torch.from_numpy(A), torch.from_numpy(np.ascontiguousarray(B.T))        # the reference takes B [K, N]
+        for _ in range(warmup):
+            ref.fp8_gemm_tiled(At[:8], Bt, 1.0, 1.0)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            ref.fp8_gemm_tiled(At, Bt, 1.0, 1.0)
+        dt = (time.perf_counter() - t0) / steps
+        out.update(value=2.0 * R * N * K / dt / 1e12, kind="reference", seconds=dt,
+                   sample=f"reference fp8_gemm_tiled (tilelang/gemm/gemm_kernels.py:96-113), first {R} activation rows x full "
+                          f"N={N}, K={K}, dequantised operands, {steps} step(s)")
+    if ref is None or want_port:
+        R = rows_port
+        _, _, port = cpu_operands(name, R)
+        for _ in range(min(warmup, 1)):
+            port()
+        n = steps if ref is None else 1
+        t0 = time.perf_counter()
+        for _ in range(n):
+            port()
+        dt = (time.perf_counter() - t0) / n
+        val = 2.0 * R * N * K / dt / 1e12
+        sample = f"numpy restatement (dequantise + fp32 GEMM), first {R} activation rows x full N={N}, K={K}"
+        if ref is None:
+            out.update(value=val, kind="port", seconds=dt, sample=sample)
+        else:
+            out["port"] = {"value": val, "unit": "TFLOP/s", "seconds": dt, "sample": sample}
+    return out
 
 
 def run_reference(args):
@@ -321,40 +448,280 @@ def run_reference(args):
     if rank != 0:
         return
     cfg = WORKLOADS[args.workload]
-    rows = 512 if not cfg.get("moe") else 512
-    val, cores, dt, sample = cpu_baseline(args.workload, rows, steps=args.steps, warmup=min(args.warmup, 2))
+    steps = args.steps if args.steps is not None else 5
+    warmup = args.warmup if args.warmup is not None else 1
+    cb = cpu_arm(args.workload, steps=steps, warmup=min(warmup, 2), want_port=False)
+    sets = args.sets
     line = {
-        "impl": "reference", "metric": "gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE_NAME[cfg["kind"]], "data": "synthetic",
-        "config": {"workload": args.workload, **{k: cfg[k] for k in ("M", "K", "N") if k in cfg},
-                   "note": "CPU port of the reference emulation (oracle), bounded sample"},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": "gemm_tflops", "value": cb["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": cb["seconds"] * 1e3, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": DTYPE_NAME[cfg["kind"]], "data": "synthetic",
+        "config": workload_config(args.workload, args.scaling, sets),
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+
+class Timer:
+    """Device timing of one workload: K-step blocks between barriers, repeated; max over ranks."""
+
+    def __init__(self, dist, device, rank, world):
+        self.dist, self.device, self.rank, self.world = dist, device, rank, world
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce_max(self, values):
+        t = torch.tensor(values, dtype=torch.float64, device=self.device)
+        if self.dist is not None:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def gather(self, value):
+        t = torch.tensor([value], dtype=torch.float64, device=self.device)
+        if self.dist is None:
+            return [value]
+        out = [torch.zeros_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t)
+        return [o.item() for o in out]
+
+    def block(self, run_steps, K):
+        """One K-step block: barrier + synchronize on both sides, CUDA events on the launching stream."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        e0.record()
+        run_steps(K)
+        e1.record()
+        self.barrier()
+        return e0.elapsed_time(e1)
+
+    def blocks(self, run_steps, K, min_seconds, max_repeats=2000):
+        """Repeats the K-step block until the timed region (sum of the blocks) reaches `min_seconds`.
+        The number of repeats is fixed from the first block (max over ranks) so that all ranks agree.
+        Returns the per-block times in ms: (max over ranks, this rank's own)."""
+        mine = [self.block(run_steps, K)]
+        first = self.reduce_max(mine)[0]
+        repeats = int(min(max_repeats, max(0, np.ceil(min_seconds * 1e3 / max(first, 1e-3)) - 1)))
+        mine += [self.block(run_steps, K) for _ in range(repeats)]
+        return self.reduce_max(mine), mine
+
+
+def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, full):
+    """Times one workload.  `full`: also the end-to-end path and per-rank detail (the headline workload)."""
+    from dsl_tool_b200 import _lib
+    rank, world, device = timer.rank, timer.world, timer.device
+    wl = build_workload(name, rank, world, device, sets, strong=strong)
+    quant, gemm = split_step(wl)
+    step = wl["step"]
+    decode = wl["M"] <= 128 and not wl["moe"]
+
+    for i in range(W):
+        step(i)
+    _lib.check_status(device)
+
+    def run_eager(n):
+        for i in range(n):
+            step(i)
+
+    runner = run_eager
+    graphs = None
+    if graph:
+        # the same steps, captured once per input set and replayed: device time without host launch gaps
+        side = torch.cuda.Stream()
+        graphs = []
+        with torch.cuda.stream(side):
+            for i in range(sets):
+                step(i)                               # this stream's scratch exists before capture
+            torch.cuda.synchronize()
+            for i in range(sets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    keep = step(i)
+                graphs.append((g, keep))
+            for i in range(W):
+                graphs[i % sets][0].replay()
+            torch.cuda.synchronize()
+
+        def run_graph(n):
+            side.wait_stream(torch.cuda.current_stream())      # the block's start event comes first
+            with torch.cuda.stream(side):
+                for i in range(n):
+                    graphs[i % sets][0].replay()
+            torch.cuda.current_stream().wait_stream(side)
+        runner = run_graph
+
+    mark0 = sampler.mark() if sampler is not None else 0
+    times, mine = timer.blocks(runner, K, min_seconds)
+    # the kernels alone: same steps, an event between quantise and GEMM, straight after the timed blocks
+    kk = min(K, 50)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(kk)]
+    for i in range(kk):
+        ev[i][0].record()
+        q = quant(i)
+        ev[i][1].record()
+        gemm(i, q)
+        ev[i][2].record()
+    torch.cuda.synchronize()
+    mark1 = sampler.mark() if sampler is not None else 0
+    gemm_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    quant_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    _lib.check_status(device)
+
+    ms_blocks = [t / K for t in times]
+    ms_med = statistics.median(ms_blocks)
+    gemm_ms_max, quant_ms_max = timer.reduce_max([gemm_ms, quant_ms])
+    flops_all = sum(timer.gather(wl["flops"]))
+    per_rank_ms = timer.gather(statistics.median(t / K for t in mine))
+    per_rank_gemm, per_rank_quant = timer.gather(gemm_ms), timer.gather(quant_ms)
+
+    bf16_peak, bf16_sus, hbm_peak, basis = measured_peaks()
+    kind = wl["kind"]
+    rec = {
+        "workload": name, "format": kind, "M": wl["M"], "K": wl["K"], "N": wl["N"],
+        "value": flops_all / (ms_med * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_med,
+        "burst": {"value": flops_all / (ms_blocks[0] * 1e-3) / 1e12, "ms_per_step": ms_blocks[0]},
+        "repeats": len(ms_blocks), "steps": K, "timed_region_s": sum(times) / 1e3,
+        "ms_per_step_min_median_max": [min(ms_blocks), ms_med, max(ms_blocks)],
+        "kernel_ms": gemm_ms_max, "quant_kernel_ms": quant_ms_max, "cuda_graph": bool(graph),
+        "host_gap_ms": max(0.0, ms_med - gemm_ms_max - quant_ms_max),
+    }
+    achieved = wl["flops"] / (gemm_ms * 1e-3) / 1e12
+    peak = bf16_peak * PEAK_MULT[kind]
+    tensor = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+              "frac_of_stated_peak": achieved / STATED_PEAK[kind], "traffic": NCU_TRAFFIC.get(name), "kernel": "gemm",
+              "kernel_ms": gemm_ms, "quant_kernel_ms": quant_ms,
+              "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"}
+    if bf16_sus:
+        tensor["frac_of_sustained"] = achieved / (bf16_sus * PEAK_MULT[kind])
+    if decode and kind in ("nvfp4", "mxfp4"):
+        # weight streaming: the step is bound by HBM; algorithmic bytes = operands + scales + output, each once
+        sfdiv = 16 if kind == "nvfp4" else 32
+        step_bytes = (wl["M"] + wl["N"]) * wl["K"] * (0.5 + 1.0 / sfdiv) + 2.0 * wl["M"] * wl["N"] + 2.0 * wl["M"] * wl["K"]
+        gbs = step_bytes / (ms_med * 1e-3) / 1e9
+        rec["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak,
+                           "frac_of_stated_peak": gbs / STATED_HBM, "traffic": NCU_TRAFFIC.get(name),
+                           "kernel": "activation quantise + weight-streaming gemm (whole step)", "bytes_per_step": step_bytes,
+                           "peak_basis": f"{basis} HBM copy {hbm_peak} GB/s"}
+        rec["roofline_tensor"] = tensor
+    else:
+        rec["roofline"] = tensor
+    if sampler is not None:
+        rec["clocks"] = sampler.summary(mark0, mark1)
+    if world > 1:
+        rec["per_rank"] = {"ms_per_step": per_rank_ms, "gemm_ms": per_rank_gemm, "quant_ms": per_rank_quant,
+                           "host_gap_ms": [max(0.0, a - b - c) for a, b, c in zip(per_rank_ms, per_rank_gemm, per_rank_quant)]}
+    if wl.get("layer"):
+        launches = 9
+    elif wl.get("split"):
+        launches = 7
+    else:
+        launches = {"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
+                    "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]
+    rec["launches_per_step"] = launches
+    rec["gpu_launches"] = launches * (K * len(ms_blocks) + kk)
+    if full:
+        rec["_wl"] = wl
+        rec["_flops_all"] = flops_all
+    else:
+        del wl, graphs
+        torch.cuda.empty_cache()
+    return rec
+
+
+def measure_e2e(wl, timer, K_steps):
+    """The step through the public callable with host buffers: H2D of the activations and D2H of the result inside
+    the timed region, pipelined by HostPipeline; plus one step at a time (latency of a single call)."""
+    from dsl_tool_b200.host_io import HostPipeline
+    device = timer.device
+    host_a = [torch.empty_like(wl["acts"][0], device="cpu").pin_memory() for _ in range(2)]
+    for j, h in enumerate(host_a):
+        h.copy_(wl["acts"][j % len(wl["acts"])])
+    dev_a = torch.empty_like(wl["acts"][0])
+    out_cols = wl["N"] // 2 if wl.get("act") else wl["N"]
+    if wl.get("layer"):
+        host_out = torch.empty((wl["out_rows"], wl["out_cols"]), dtype=torch.bfloat16).pin_memory()
+    elif wl.get("out") == "nvfp4":
+        host_out = torch.empty((wl["M"], out_cols // 2), dtype=torch.uint8).pin_memory()
+    else:
+        host_out = torch.empty((wl["M"], out_cols), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(4, min(K_steps, 12))
+    for i in range(2):
+        dev_a.copy_(host_a[i % 2], non_blocking=True)
+        host_out.copy_(wl["step"](i, dev_a), non_blocking=True)
+    timer.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(3):
+        dev_a.copy_(host_a[i % 2], non_blocking=True)
+        host_out.copy_(wl["step"](i, dev_a), non_blocking=True)
+    e1.record()
+    timer.barrier()
+    serial_ms = e0.elapsed_time(e1) / 3
+    cell = [0]
+    pipe = HostPipeline(lambda a: wl["step"](cell[0], a), device)
+    host_outs = [host_out, torch.empty_like(host_out).pin_memory()]
+    for i in range(3):
+        cell[0] = i
+        pipe.submit(host_a[i % 2], host_outs[i % 2])
+    pipe.join()
+    timer.barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        cell[0] = i
+        pipe.submit(host_a[i % 2], host_outs[i % 2])
+    pipe.join()
+    e1.record()
+    timer.barrier()
+    e2e_ms = timer.reduce_max([e0.elapsed_time(e1) / e2e_steps])[0]
+    return e2e_ms, serial_ms, wl["acts"][0].numel() * 2, host_out.numel() * host_out.element_size()
+
+
+def host_cost_us(wl, n=200):
+    """Host time of one call of the public callable with the stream left to drain first (time.perf_counter
+    around the call; nothing waits for the GPU inside)."""
+    step = wl["step"]
+    for i in range(5):
+        step(i)
+    torch.cuda.synchronize()
+    best = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        for i in range(n):
+            step(i)
+        best.append((time.perf_counter() - t0) / n * 1e6)
+        torch.cuda.synchronize()
+    return min(best)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="fp8_groupwise_llama8b_mlp", choices=sorted(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=None, help="steps per timed block (default 50; reference arm 5)")
+    ap.add_argument("--warmup", type=int, default=None, help="untimed warm-up steps (default 5, at least 3)")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--sets", type=int, default=4, help="rotating input sets (keeps operands out of L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak: every rank holds a full-size shard (default); strong: the one problem is split "
-                         "across ranks (columns / experts)")
+    ap.add_argument("--no-sweep", action="store_true", help="only the headline workload")
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="the K-step block is repeated until the timed region is this long")
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="strong (default): the one problem is split across the ranks (columns / experts); "
+                         "weak: every rank holds a full-size shard")
     ap.add_argument("--graph", action="store_true",
                     help="replay each step (quantise + GEMM) from a CUDA graph: removes host launch gaps, "
                          "which dominate the decode-sized workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
-    if args.warmup < 3:
-        args.warmup = 3
+    K_steps = args.steps if args.steps is not None else 50
+    W = max(3, args.warmup if args.warmup is not None else 5)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -368,182 +735,65 @@ def main():
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
+    timer = Timer(dist, device, rank, world)
+    strong = args.scaling == "strong"
+    sampler = ClockSampler(local).start() if rank == 0 else None
 
-    from dsl_tool_b200 import _lib
-    wl = build_workload(args.workload, rank, world, device, args.sets, strong=args.scaling == "strong")
-    quant, gemm = split_step(wl)
-    K_steps, W = args.steps, args.warmup
+    cfg0 = WORKLOADS[args.workload]
+    decode0 = (not cfg0.get("moe")) and cfg0.get("M", 1 << 30) <= 128
+    head = measure(args.workload, args, timer, sampler, K_steps, W, args.min_seconds, args.graph or False, strong, args.sets, True)
+    wl = head.pop("_wl")
+    flops_all = head.pop("_flops_all")
+    clocks = head.pop("clocks", None)
+    e2e_ms, serial_ms, h2d, d2h = measure_e2e(wl, timer, K_steps)
+    host_us = host_cost_us(wl) if not wl.get("layer") else None
+    del wl
+    torch.cuda.empty_cache()
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing ------------------------------------------------------------
-    for i in range(W):
-        gemm(i, quant(i))
-    _lib.check_status(device)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(K_steps)]
-    barrier()
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
-    t_start.record()
-    for i in range(K_steps):
-        ev[i][0].record()
-        q = quant(i)
-        ev[i][1].record()
-        out = gemm(i, q)
-        ev[i][2].record()
-    t_end.record()
-    barrier()
-    total_ms = t_start.elapsed_time(t_end)
-    gemm_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    quant_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    graph_ms = None
-    if args.graph:
-        # same steps, captured once per input set and replayed: device time without host gaps
-        side = torch.cuda.Stream()
-        graphs = []
-        with torch.cuda.stream(side):
-            for i in range(args.sets):
-                gemm(i, quant(i))                     # this stream's scratch exists before capture
-            torch.cuda.synchronize()
-            for i in range(args.sets):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    keep = gemm(i, quant(i))
-                graphs.append((g, keep))
-            for i in range(W):
-                graphs[i % args.sets][0].replay()
-            barrier()
-            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            g0.record()
-            for i in range(K_steps):
-                graphs[i % args.sets][0].replay()
-            g1.record()
-            barrier()
-            graph_ms = g0.elapsed_time(g1) / K_steps
-        total_ms = graph_ms * K_steps
-    clocks = sampler.stop() if rank == 0 else None
-    _lib.check_status(device)
-
-    # ---- end to end: activations from pinned host memory, result back to the host -----------
-    host_a = [torch.empty_like(wl["acts"][0], device="cpu").pin_memory() for _ in range(2)]
-    for j, h in enumerate(host_a):
-        h.copy_(wl["acts"][j % len(wl["acts"])])
-    dev_a = torch.empty_like(wl["acts"][0])
-    out_cols = wl["N"] // 2 if wl.get("act") else wl["N"]
-    if wl.get("layer"):
-        out_cols = wl["out_cols"]
-        host_out = torch.empty((wl["out_rows"], out_cols), dtype=torch.bfloat16).pin_memory()
-    elif wl.get("out") == "nvfp4":
-        host_out = torch.empty((wl["M"], out_cols // 2), dtype=torch.uint8).pin_memory()
-    else:
-        host_out = torch.empty((wl["M"], out_cols), dtype=torch.bfloat16).pin_memory()
-    e2e_steps = max(4, min(K_steps, 12))
-    for i in range(2):
-        dev_a.copy_(host_a[i % 2], non_blocking=True)
-        host_out.copy_(wl["step"](i, dev_a), non_blocking=True)
-    barrier()
-    # one step at a time: copy in, compute, copy out on one stream (the latency of a single call)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(3):
-        dev_a.copy_(host_a[i % 2], non_blocking=True)
-        host_out.copy_(wl["step"](i, dev_a), non_blocking=True)
-    e1.record()
-    barrier()
-    e2e_serial_ms = e0.elapsed_time(e1) / 3
-    # throughput: the same steps through the library's host pipeline (copy-in of step i+1 and copy-out of
-    # step i-1 overlap the compute of step i); every step's copies are inside the timed region
-    from dsl_tool_b200.host_io import HostPipeline
-    cell = [0]
-    pipe = HostPipeline(lambda a: wl["step"](cell[0], a), device)
-    host_outs = [host_out, torch.empty_like(host_out).pin_memory()]
-    for i in range(3):
-        cell[0] = i
-        pipe.submit(host_a[i % 2], host_outs[i % 2])
-    pipe.join()
-    barrier()
-    e0.record()
-    for i in range(e2e_steps):
-        cell[0] = i
-        pipe.submit(host_a[i % 2], host_outs[i % 2])
-    pipe.join()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
-
-    # ---- aggregate over ranks (max time, summed work) ------------------------------------------
-    stats = torch.tensor([total_ms, e2e_ms, wl["flops"], gemm_ms, quant_ms], dtype=torch.float64, device=device)
-    if dist is not None:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, e2e_ms, gemm_ms, quant_ms = mx[0].item(), mx[1].item(), mx[3].item(), mx[4].item()
-        flops_all = sm[2].item()
-    else:
-        flops_all = wl["flops"]
+    sweep = []
+    if not args.no_sweep and args.workload == DEFAULT_WORKLOAD:
+        names = SWEEP_1GPU if world == 1 else SWEEP_SHARDED
+        for name in names:
+            c = WORKLOADS[name]
+            is_decode = (not c.get("moe")) and not c.get("tokens_in") and not c.get("layer") and c.get("M", 1 << 30) <= 128
+            big = c.get("moe") or c.get("tokens_in") or c.get("layer") or c.get("K", 0) * c.get("N", 0) >= (1 << 27)
+            try:
+                rec = measure(name, args, timer, sampler, min(K_steps, 20 if big else 50), 3, 0.25, is_decode, strong,
+                              2 if big else args.sets, False)
+            except Exception as exc:     # a sweep entry must not take the headline down with it
+                rec = {"workload": name, "error": f"{type(exc).__name__}: {exc}"}
+            sweep.append(rec)
+    clocks_all = sampler.stop() if sampler is not None else None
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    ms_per_step = total_ms / K_steps
-    value = flops_all / (ms_per_step * 1e-3) / 1e12
-    bf16_peak, hbm_peak, basis = measured_peaks()
-    kind = wl["kind"]
-    achieved = wl["flops"] / (gemm_ms * 1e-3) / 1e12
-    peak = bf16_peak * PEAK_MULT[kind]
-    decode = wl["M"] <= 128 and not wl["moe"]
-    if decode and kind in ("nvfp4", "mxfp4"):
-        # weight streaming: the step is bound by HBM; algorithmic bytes = operands + scales + output, each once
-        sfdiv = 16 if kind == "nvfp4" else 32
-        step_bytes = (wl["M"] + wl["N"]) * wl["K"] * (0.5 + 1.0 / sfdiv) + 2.0 * wl["M"] * wl["N"] + 2.0 * wl["M"] * wl["K"]
-        hbm = {"bound": "hbm", "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
-               "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak, "traffic": NCU_TRAFFIC.get(args.workload),
-               "kernel": "activation quantise + weight-streaming gemm (whole step)", "bytes_per_step": step_bytes,
-               "peak_basis": f"{basis} HBM copy {hbm_peak} GB/s"}
-    else:
-        hbm = None
     line = {
-        "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-        "dtype": DTYPE_NAME[kind], "data": "synthetic",
-        "config": {"workload": args.workload, "M": wl["M"], "K": wl["K"], "N": wl["N"],
-                   "out": ("bf16" if not wl.get("act") else "bf16 [M, N/2] = silu(gate) * up, folded in the GEMM epilogue")
-                   if not wl.get("out") else "NVFP4 [M, N/2] = quantise(silu(gate) * up), both folded in the GEMM epilogue",
-                   "moe": wl["moe"], "per_rank": ("own weight shard / experts of this size, no collective" if args.scaling == "weak" else
-                                "this rank's column range / experts of the one problem, no collective"),
-                   "step": "activation quantise + GEMM, weights quantised once",
-                   "l2": f"inputs rotate over {args.sets} sets (larger than the 126 MB L2)"},
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak, "traffic": NCU_TRAFFIC.get(args.workload),
-                     "kernel": "gemm", "kernel_ms": gemm_ms, "quant_kernel_ms": quant_ms,
-                     "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"},
-        "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "h2d_bytes_per_step": wl["acts"][0].numel() * 2, "d2h_bytes_per_step": host_out.numel() * host_out.element_size(),
-                "ms_per_step": e2e_ms, "single_step_ms": e2e_serial_ms,
+        "metric": "gemm_tflops", "value": head["value"], "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+        "dtype": DTYPE_NAME[head["format"]], "data": "synthetic",
+        "config": workload_config(args.workload, args.scaling, args.sets),
+        "repeats": head["repeats"], "timed_region_s": head["timed_region_s"],
+        "ms_per_step_min_median_max": head["ms_per_step_min_median_max"], "burst": head["burst"],
+        "roofline": head["roofline"],
+        "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "single_step_ms": serial_ms,
                 "how": "HostPipeline: pinned host buffers, copy-in / compute / copy-out on three streams, two staging buffers"},
-        # kernels of this library per step: quantiser passes + one GEMM kernel (NVFP4 tensors of up to
-        # 2^18 elements are quantised by a single launch, larger ones by an amax pass + a quantise pass)
-        "gpu_launches": K_steps * 9 if wl.get("layer") else K_steps * 7 if wl.get("split") else K_steps * ({"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
-                                    "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]),
+        "host_us_per_call": host_us,
+        "gpu_launches": head["gpu_launches"], "launches_per_step": head["launches_per_step"],
         "cuda_graph": bool(args.graph),
-        "clocks": clocks,
+        "clocks": clocks if clocks is not None else clocks_all,
     }
-    if hbm is not None:
-        line["roofline_tensor"] = line["roofline"]
-        line["roofline"] = hbm
+    if "roofline_tensor" in head:
+        line["roofline_tensor"] = head["roofline_tensor"]
+    if "per_rank" in head:
+        line["per_rank"] = head["per_rank"]
+        line["kernel_ms"], line["quant_kernel_ms"], line["host_gap_ms"] = head["kernel_ms"], head["quant_kernel_ms"], head["host_gap_ms"]
+    if sweep:
+        line["sweep"] = sweep
     if not args.no_cpu_baseline and world == 1:
-        rows = 512
-        val, cores, dt, sample = cpu_baseline(args.workload, rows)
-        line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
-                                "seconds": dt}
+        line["cpu_baseline"] = cpu_arm(args.workload, steps=1, warmup=1)
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -30,7 +30,7 @@ def load_reference(root):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden", "reference_py_activations.npz"))
     args = ap.parse_args()
     ref = load_reference(args.reference)

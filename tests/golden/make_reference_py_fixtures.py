@@ -31,7 +31,7 @@ def load_reference(root):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden", "reference_py.npz"))
     args = ap.parse_args()
     ref = load_reference(args.reference)
