@@ -557,21 +557,26 @@ def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, 
             torch.cuda.current_stream().wait_stream(side)
         runner = run_graph
 
+    # the kernels alone: same steps with an event between quantise and GEMM - once before the timed blocks
+    # (the part is cool: burst clocks) and once straight after them (the clocks the part sustains)
+    kk = min(K, 50)
+
+    def kernel_pass():
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(kk)]
+        for i in range(kk):
+            ev[i][0].record()
+            q = quant(i)
+            ev[i][1].record()
+            gemm(i, q)
+            ev[i][2].record()
+        torch.cuda.synchronize()
+        return (statistics.mean(e[1].elapsed_time(e[2]) for e in ev), statistics.mean(e[0].elapsed_time(e[1]) for e in ev))
+
+    gemm_ms_burst, _ = kernel_pass() if full else (None, None)
     mark0 = sampler.mark() if sampler is not None else 0
     times, mine = timer.blocks(runner, K, min_seconds)
-    # the kernels alone: same steps, an event between quantise and GEMM, straight after the timed blocks
-    kk = min(K, 50)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(kk)]
-    for i in range(kk):
-        ev[i][0].record()
-        q = quant(i)
-        ev[i][1].record()
-        gemm(i, q)
-        ev[i][2].record()
-    torch.cuda.synchronize()
+    gemm_ms, quant_ms = kernel_pass()
     mark1 = sampler.mark() if sampler is not None else 0
-    gemm_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    quant_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
     _lib.check_status(device)
 
     ms_blocks = [t / K for t in times]
@@ -593,13 +598,20 @@ def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, 
         "host_gap_ms": max(0.0, ms_med - gemm_ms_max - quant_ms_max),
     }
     achieved = wl["flops"] / (gemm_ms * 1e-3) / 1e12
-    peak = bf16_peak * PEAK_MULT[kind]
+    # The kernel is timed inside a region of a second or more (sustained clocks, usually at the power cap), so the
+    # denominator is the cuBLAS bf16 rate measured the same way; the headline workload also carries the pair
+    # "timed cool / burst peak".  Sweep entries run a quarter of a second each: they are compared with the burst peak.
+    sustained = full and bool(bf16_sus) and sum(times) >= 900.0
+    base = bf16_sus if sustained else bf16_peak
+    peak = base * PEAK_MULT[kind]
     tensor = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
               "frac_of_stated_peak": achieved / STATED_PEAK[kind], "traffic": NCU_TRAFFIC.get(name), "kernel": "gemm",
               "kernel_ms": gemm_ms, "quant_kernel_ms": quant_ms,
-              "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"}
-    if bf16_sus:
-        tensor["frac_of_sustained"] = achieved / (bf16_sus * PEAK_MULT[kind])
+              "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 {'sustained' if sustained else 'burst'} {base} TFLOP/s"}
+    if gemm_ms_burst:
+        ab = wl["flops"] / (gemm_ms_burst * 1e-3) / 1e12
+        tensor["burst"] = {"achieved": ab, "peak": bf16_peak * PEAK_MULT[kind], "frac": ab / (bf16_peak * PEAK_MULT[kind]),
+                           "kernel_ms": gemm_ms_burst, "peak_basis": f"{PEAK_MULT[kind]:g} x {basis} bf16 burst {bf16_peak} TFLOP/s"}
     if decode and kind in ("nvfp4", "mxfp4"):
         # weight streaming: the step is bound by HBM; algorithmic bytes = operands + scales + output, each once
         sfdiv = 16 if kind == "nvfp4" else 32
@@ -625,7 +637,7 @@ def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, 
         launches = {"fp8": 3, "fp8_block128": 2, "mxfp4": 2, "bf16": 1,
                     "nvfp4": 2 if (not wl["moe"] and wl["M"] * wl["K"] <= (256 << 10)) else 3}[kind]
     rec["launches_per_step"] = launches
-    rec["gpu_launches"] = launches * (K * len(ms_blocks) + kk)
+    rec["gpu_launches"] = launches * (K * len(ms_blocks) + kk * (2 if full else 1))
     if full:
         rec["_wl"] = wl
         rec["_flops_all"] = flops_all

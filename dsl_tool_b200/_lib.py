@@ -57,6 +57,21 @@ class Epilogue(ctypes.Structure):
     ]
 
 
+class Weight(ctypes.Structure):
+    """dsl_weight of include/dslgemm.h."""
+    _fields_ = [
+        ("format", ctypes.c_int),
+        ("groups", ctypes.c_int),
+        ("n", ctypes.c_int),
+        ("k", ctypes.c_int),
+        ("q", ctypes.c_void_p),
+        ("scale", ctypes.c_void_p),
+        ("global_scale", ctypes.c_void_p),
+    ]
+
+
+W_FP8, W_FP8_BLOCK128, W_NVFP4, W_MXFP4, W_BF16 = 0, 1, 2, 3, 4
+
 _lib: Optional[ctypes.CDLL] = None
 _lock = threading.Lock()
 
@@ -76,6 +91,9 @@ _SIGNATURES = {
     "dsl_gemm_fp4_static_scratch": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i,
                                          ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_workspace_bytes": (ctypes.c_size_t, [_i, _ll, _i, _i, _i]),
+    "dsl_linear_scratch_bytes": (ctypes.c_size_t, [_i, _ll, _i, _i]),
+    "dsl_linear": (_i, [_vp, _i, _ll, ctypes.POINTER(Weight), _vp, _vp, ctypes.c_size_t, _vp, _ll,
+                        ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_quant_fp4_ref32": (_i, [_vp, _i, _ll, _vp, _vp, _vp]),
     "dsl_gemm_fp4_ref32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dsl_moe_route": (_i, [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
@@ -190,6 +208,41 @@ def workspace(device: torch.device, need: int = WORKSPACE_BYTES) -> Optional[tor
         t = torch.empty(max(int(need), WORKSPACE_BYTES), dtype=torch.uint8, device=device)
         _workspace[key] = t
     return t
+
+
+class ActArena:
+    """Scratch for the quantised activations of `dsl_linear`, one per (device, stream).  The GEMM of a call
+    consumes what the quantiser of the same call wrote, so calls issued in order on one stream share it; the
+    lock keeps two host threads that launch on the same stream from interleaving their two launches."""
+
+    def __init__(self) -> None:
+        self.buf: Optional[torch.Tensor] = None
+        self.lock = threading.Lock()
+        self.retired: list = []      # outgrown buffers stay alive: a captured CUDA graph may still point at them
+
+    def get(self, device: torch.device, need: int) -> torch.Tensor:
+        buf = self.buf
+        if buf is None or buf.numel() < need:
+            if torch.cuda.is_current_stream_capturing():
+                # memory allocated under capture belongs to that graph's pool: use it for this call only
+                return torch.empty(need, dtype=torch.uint8, device=device)
+            if buf is not None:
+                self.retired.append(buf)
+            buf = torch.empty(max(int(need * 1.25), 1 << 20), dtype=torch.uint8, device=device)
+            self.buf = buf
+        return buf
+
+
+_arenas: Dict[tuple, ActArena] = {}
+
+
+def act_arena(device: torch.device, stream: int) -> ActArena:
+    key = (device.index, stream)
+    a = _arenas.get(key)
+    if a is None:
+        with _lock:
+            a = _arenas.setdefault(key, ActArena())
+    return a
 
 
 def check_status(device: Optional[torch.device] = None) -> None:

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libdslgemm.so")
-SOURCES = ["quant.cu", "gemm.cu", "gemm_pair.cu", "gemm_decode.cu", "gemm_groupwise.cu", "gemm_groupwise_pair.cu", "abi.cu", "static_scratch.cu", "fp4_ref32.cu", "moe.cu"]
+SOURCES = ["quant.cu", "gemm.cu", "gemm_pair.cu", "gemm_decode.cu", "gemm_groupwise.cu", "gemm_groupwise_pair.cu", "abi.cu", "static_scratch.cu", "fp4_ref32.cu", "moe.cu", "linear.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC,

@@ -384,8 +384,27 @@ static EncodeTiledFn get_encoder() {
 }
 
 // Byte tensor [d2][d1][d0] (d0 contiguous) with a box of box0 x box1 x 1 and the 128-byte swizzle.
+// An encoded map is a pure function of these seven values, so each host thread keeps the last few it
+// encoded (weights and reused activation buffers come back call after call) and skips the driver call.
 bool make_tmap_u8(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box0,
                   uint32_t box1) {
+    struct Entry {
+        const void* base;
+        uint64_t d0, d1, d2;
+        uint32_t box0, box1;
+        bool valid;
+        CUtensorMap map;
+    };
+    constexpr int kSlots = 64;
+    thread_local Entry cache[kSlots] = {};
+    uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+    h = (h ^ (d0 * 0x9E3779B97F4A7C15ull) ^ (d1 * 0xC2B2AE3D27D4EB4Full) ^ (d2 << 7) ^ (static_cast<uint64_t>(box1) << 20) ^ box0) *
+        0xD6E8FEB86659FD93ull;
+    Entry& e = cache[(h >> 40) % kSlots];
+    if (e.valid && e.base == base && e.d0 == d0 && e.d1 == d1 && e.d2 == d2 && e.box0 == box0 && e.box1 == box1) {
+        *m = e.map;
+        return true;
+    }
     EncodeTiledFn enc = get_encoder();
     if (enc == nullptr) return false;
     cuuint64_t dims[3] = {d0, d1, d2};
@@ -396,7 +415,11 @@ bool make_tmap_u8(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, ui
     CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    if (r != CUDA_SUCCESS) return false;
+    e.base = base; e.d0 = d0; e.d1 = d1; e.d2 = d2; e.box0 = box0; e.box1 = box1;
+    e.map = *m;
+    e.valid = true;
+    return true;
 }
 
 int sm_count() {

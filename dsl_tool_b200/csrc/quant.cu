@@ -331,8 +331,12 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict_
     const int rpb = 256 >> log2_cp;
     const long long row_blocks = (M + rpb - 1) / rpb;
     const int kc = blockIdx.y * 256 + (threadIdx.x & ((1 << log2_cp) - 1));
-    // grid-stride over row blocks: the group tables above are built once per CTA, not once per row
-    for (long long rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+    // grid-stride over row blocks: the group tables above are built once per CTA, not once per row.
+    // After an amax pass the END of the tensor is what the L2 still holds (that pass walks it front to
+    // back), so this pass then walks the row blocks back to front and finds much of its input there.
+    const bool backwards = FMT == 0 && amax_bits != nullptr;
+    for (long long it = blockIdx.x; it < row_blocks; it += gridDim.x) {
+    const long long rb = backwards ? row_blocks - 1 - it : it;
     const long long row = rb * rpb + (threadIdx.x >> log2_cp);
     const bool valid = row < M && kc < cpr;
     const size_t id = static_cast<size_t>(row) * cpr + kc;

@@ -267,6 +267,75 @@ def gemm_bf16_raw(a: torch.Tensor, b_nk: torch.Tensor, *, n: int, out_dtype=torc
 # quantise-and-multiply on one packed weight (shared by the public callables)
 # --------------------------------------------------------------------------------------
 
+_W_CODES = {"fp8": _lib.W_FP8, "fp8_block128": _lib.W_FP8_BLOCK128, "nvfp4": _lib.W_NVFP4, "mxfp4": _lib.W_MXFP4, "bf16": _lib.W_BF16}
+_OP_OF_FORMAT = {"fp8": _lib.OP_GEMM_FP8, "fp8_block128": _lib.OP_GEMM_FP8_GROUPWISE, "nvfp4": _lib.OP_GEMM_FP4_NV,
+                 "mxfp4": _lib.OP_GEMM_FP4_MX, "bf16": _lib.OP_GEMM_BF16}
+
+
+def _weight_desc(w: PackedWeight) -> "_lib.Weight":
+    """The weight's dsl_weight struct, built once and kept on the PackedWeight (rebuilt if its tensors were swapped)."""
+    d = getattr(w, "_cdesc", None)
+    if d is None or d.q != w.q.data_ptr():
+        d = _lib.Weight()
+        d.format, d.groups, d.n, d.k = _W_CODES[w.format], w.groups, w.n, w.k
+        d.q = w.q.data_ptr()
+        d.scale = None if w.scale is None else w.scale.data_ptr()
+        d.global_scale = None if w.global_scale is None else w.global_scale.data_ptr()
+        w._cdesc = d
+        w._scratch_need = {}
+    return d
+
+
+def _linear_one_call(a: torch.Tensor, w: PackedWeight, out_dtype, offs: Optional[torch.Tensor], row_scale, col_scale,
+                     activation: Optional[str], out_global_scale: Scalar):
+    """Quantise + GEMM through the single C entry point `dsl_linear`: one call into the library, the quantised
+    activations in a per-stream arena instead of fresh allocations."""
+    dev = a.device
+    lib = _lib.lib()
+    M = a.shape[0]
+    desc = _weight_desc(w)
+    groups = w.groups
+    nc = _out_cols(w.n, activation)
+    keep: list = []
+    ep = _lib.Epilogue()
+    ep.scale_a_host = ep.scale_b_host = 1.0
+    ep.activation = _activation_code(activation)
+    if row_scale is not None:
+        row_scale = row_scale.detach().to(device=dev, dtype=torch.float32).contiguous()
+        ep.row_scale = row_scale.data_ptr()
+    if col_scale is not None:
+        col_scale = col_scale.detach().to(device=dev, dtype=torch.float32).contiguous()
+        ep.col_scale = col_scale.data_ptr()
+    switch = torch.cuda.current_device() != dev.index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        if groups == 1:                    # row groups never use scratch; the library says what a dense problem can use
+            ws = _lib.workspace(dev, int(lib.dsl_workspace_bytes(_OP_OF_FORMAT[w.format], M, w.n, w.k, 1)))
+            if ws is not None:
+                ep.workspace = ws.data_ptr()
+                ep.workspace_bytes = ws.numel()
+        out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
+        need = w._scratch_need.get(M)
+        if need is None:
+            need = int(lib.dsl_linear_scratch_bytes(desc.format, M, w.k, groups))
+            if len(w._scratch_need) < 64:
+                w._scratch_need[M] = need
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        arena = _lib.act_arena(dev, stream)
+        with arena.lock:
+            buf = arena.get(dev, need) if need else None
+            rc = lib.dsl_linear(a.data_ptr(), _lib.dtype_code(a.dtype), M, ctypes.byref(desc), _lib.ptr(offs),
+                                _lib.ptr(buf), 0 if buf is None else buf.numel(), out.data_ptr(), ldc, ctypes.byref(ep),
+                                _lib.status_word(dev).data_ptr(), stream)
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
+    _lib.check(rc, "dsl_linear")
+    return ret
+
+
 def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
            expert_offsets: Optional[torch.Tensor] = None, row_scale=None, col_scale=None,
            activation: Optional[str] = None, out_global_scale: Scalar = None):
@@ -284,10 +353,18 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
         raise ValueError(f"activations must be [M, {w.k}], got {tuple(a.shape)}")
     if w.groups > 1 and expert_offsets is None:
         raise ValueError("a multi-group weight needs expert_offsets")
+    if _is_nvfp4_out(out_dtype) and w.format == "fp8_block128":
+        raise ValueError("a quantised result is not available from the group-scaled FP8 GEMM")
+    if (a.is_cuda and a.is_contiguous() and w.q.device == a.device and (w.groups > 1) == (expert_offsets is not None)
+            and (a.dtype == torch.bfloat16 if w.format == "bf16" else a.dtype in _FLOAT_DTYPES)):
+        offs = None
+        if expert_offsets is not None:
+            offs, groups = _offsets_arg(expert_offsets, a.device)
+            if groups != w.groups:
+                raise ValueError(f"expert_offsets describes {groups} groups, the weight holds {w.groups}")
+        return _linear_one_call(a, w, out_dtype, offs, row_scale, col_scale, activation, out_global_scale)
     common = dict(n=w.n, out_dtype=out_dtype, expert_offsets=expert_offsets, activation=activation)
     if _is_nvfp4_out(out_dtype):
-        if w.format == "fp8_block128":
-            raise ValueError("a quantised result is not available from the group-scaled FP8 GEMM")
         common["out_global_scale"] = out_global_scale
     if w.format == "bf16":
         return gemm_bf16_raw(a, w.q, **common)

@@ -181,6 +181,35 @@ int dsl_gemm_fp4(const uint8_t* A, const uint8_t* B, const uint8_t* sfa, const u
                  const dsl_epilogue* ep, uint32_t* status, void* stream);
 
 /*
+ * One step of the hot path in a single call: quantise / scale-pack the activations x [M, K] (`x_dtype`) in the
+ * format of the packed weight and multiply, C[M, N] = x_q @ W^T with the epilogue of the matching dsl_gemm_*
+ * entry point.  Replaces the reference's per-call sequence quantise A, quantise B, GEMM
+ * (cuda/gemm/fp8_gemm.cu:180-190, cuda/gemm/fp4_gemm.cu:181-190) for a weight that was quantised once.
+ *   w            the packed weight: q [groups * n, k bytes] K-major; scale = float[1] (DSL_W_FP8), 128x128 block
+ *                scales [groups, ceil(n/128), k/128] (DSL_W_FP8_BLOCK128) or tiled scale bytes (FP4);
+ *                global_scale = device float (NVFP4 only).  DSL_W_BF16: no quantisation, x must be bf16.
+ *   group_offsets  int32[groups + 1] device row offsets when w->groups > 1 (ragged expert groups), else ignored
+ *   act_scratch  device memory (256-byte aligned) of at least dsl_linear_scratch_bytes(format, M, k, groups) bytes
+ *                that receives the quantised activations, their scales and the amax cell; the GEMM of the same
+ *                call consumes it, so calls issued in order on one stream may share one area.  Calls that can
+ *                overlap on the GPU (different streams) need separate areas, like dsl_epilogue.workspace.
+ *   ep           as for dsl_gemm_*; scale_a / scale_b are filled in here (activation scale, weight scale) and
+ *                b_is_static is set.
+ */
+enum { DSL_W_FP8 = 0, DSL_W_FP8_BLOCK128 = 1, DSL_W_NVFP4 = 2, DSL_W_MXFP4 = 3, DSL_W_BF16 = 4 };
+typedef struct {
+    int format;                 /* DSL_W_* */
+    int groups, n, k;           /* weight is [groups, n, k] */
+    const void* q;
+    const void* scale;
+    const float* global_scale;
+} dsl_weight;
+size_t dsl_linear_scratch_bytes(int format, long long M, int K, int groups);
+int dsl_linear(const void* x, int x_dtype, long long M, const dsl_weight* w, const int* group_offsets,
+               void* act_scratch, size_t act_scratch_bytes, void* C, long long ldc, const dsl_epilogue* ep,
+               uint32_t* status, void* stream);
+
+/*
  * The reference's own FP4 container (its "NVFP4" and "MXFP4" are one format, cuda/gemm/fp4_gemm.cu:30-42):
  * e2m1 nibbles with one fp32 scale per 32 contiguous elements of the FLAT buffer.
  * dsl_quant_fp4_ref32 replaces quantize_fp32_to_nvfp4 (fp4_gemm.cu:50-90) bit for bit (scale = max(amax/6,
