@@ -102,6 +102,9 @@ _SIGNATURES = {
     "dsl_moe_dispatch_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp]),
     "dsl_moe_dispatch_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _ll, _i, _i, _vp, _vp]),
     "dsl_moe_combine": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
+    "dsl_moe_wire_bytes": (ctypes.c_size_t, [_i, _i]),
+    "dsl_moe_pack_wire_fp4": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "dsl_moe_unpack_wire_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_selftest_static_scratch_copy": (_i, [_vp, ctypes.c_size_t, ctypes.c_size_t, _i, _vp]),
     "dsl_selftest_bounded_wait": (_i, [_vp, ctypes.c_uint, _vp]),

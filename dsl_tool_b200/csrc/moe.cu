@@ -189,6 +189,52 @@ moe_dispatch_fp4_kernel(const uint8_t* __restrict__ q_in, const uint8_t* __restr
         *reinterpret_cast<uint32_t*>(d_tile + static_cast<size_t>(a) * 512) = *reinterpret_cast<const uint32_t*>(s_tile + static_cast<size_t>(a) * 512);
 }
 
+// ---- rows on the wire (token all-to-all) --------------------------------------------------------
+// A routed row travels between GPUs as one record: the packed e2m1 bytes followed by the row's scale bytes in
+// plain K order (one 32-bit word per 512-byte scale tile of the row, i.e. four scale bytes; zero padding included),
+// padded to a multiple of 16 bytes.  pack: entry i = token * k + slot -> record dest[i] (all experts, expert-sorted).
+__global__ void __launch_bounds__(256)
+moe_pack_wire_fp4_kernel(const uint8_t* __restrict__ q_in, const uint8_t* __restrict__ sf_in, const int* __restrict__ dest,
+                         int entries, int k, int row_bytes, int katoms, int wire_bytes, uint8_t* __restrict__ wire) {
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (i >= entries) return;
+    const int t = i / k;
+    const uint4* src = reinterpret_cast<const uint4*>(q_in + static_cast<size_t>(t) * row_bytes);
+    uint8_t* rec = wire + static_cast<size_t>(dest[i]) * wire_bytes;
+    uint4* dst = reinterpret_cast<uint4*>(rec);
+    for (int j = lane; j < row_bytes / 16; j += 32) dst[j] = src[j];
+    const int rin = t & 127;
+    const uint8_t* s_tile = sf_in + static_cast<size_t>(t >> 7) * katoms * 512 + (rin & 31) * 16 + (rin >> 5) * 4;
+    uint32_t* words = reinterpret_cast<uint32_t*>(rec + row_bytes);
+    const int nwords = (wire_bytes - row_bytes) / 4;
+    for (int a = lane; a < nwords; a += 32)
+        words[a] = a < katoms ? *reinterpret_cast<const uint32_t*>(s_tile + static_cast<size_t>(a) * 512) : 0u;
+}
+
+// unpack: record r (expert ids[r] of this rank, position dest[r] in this rank's expert-sorted order) -> packed row
+// dest[r] and its scale bytes in the ragged-group tile layout (every expert starts a fresh 128-row tile).
+__global__ void __launch_bounds__(256)
+moe_unpack_wire_fp4_kernel(const uint8_t* __restrict__ wire, const int* __restrict__ ids, const int* __restrict__ dest,
+                           const int* __restrict__ offsets, const int* __restrict__ tile0, int rows, int row_bytes, int katoms,
+                           int wire_bytes, uint8_t* __restrict__ q_out, uint8_t* __restrict__ sf_out) {
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const int e = ids[r];
+    const int d = dest[r];
+    const uint8_t* rec = wire + static_cast<size_t>(r) * wire_bytes;
+    const uint4* src = reinterpret_cast<const uint4*>(rec);
+    uint4* dst = reinterpret_cast<uint4*>(q_out + static_cast<size_t>(d) * row_bytes);
+    for (int j = lane; j < row_bytes / 16; j += 32) dst[j] = src[j];
+    const int rg = d - offsets[e];
+    const int tile_d = tile0[e] + (rg >> 7);
+    const int rin = rg & 127;
+    uint8_t* d_tile = sf_out + static_cast<size_t>(tile_d) * katoms * 512 + (rin & 31) * 16 + (rin >> 5) * 4;
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(rec + row_bytes);
+    for (int a = lane; a < katoms; a += 32) *reinterpret_cast<uint32_t*>(d_tile + static_cast<size_t>(a) * 512) = words[a];
+}
+
 // Plain rows (bf16 activations, E4M3 bytes, ...): same mapping, row_bytes % 16 == 0.
 __global__ void __launch_bounds__(256)
 moe_dispatch_rows_kernel(const uint8_t* __restrict__ x, const int* __restrict__ ids, const int* __restrict__ dest,
@@ -369,5 +415,47 @@ extern "C" int dsl_moe_combine(const void* y, int y_dtype, const int* ids, const
     else if (out_dtype == DSL_F32) DSL_COMBINE(__nv_bfloat16, float);
     else DSL_COMBINE(__nv_bfloat16, __nv_bfloat16);
 #undef DSL_COMBINE
+    return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" size_t dsl_moe_wire_bytes(int K, int format) {
+    if (K <= 0 || K % 32 != 0 || (format != DSL_FP4_NV && format != DSL_FP4_MX)) return 0;
+    const int nblk = format == DSL_FP4_NV ? K / 16 : K / 32;
+    const size_t raw = static_cast<size_t>(K) / 2 + 4u * static_cast<size_t>((nblk + 3) / 4);
+    return (raw + 15) / 16 * 16;
+}
+
+extern "C" int dsl_moe_pack_wire_fp4(const uint8_t* q_in, const uint8_t* sf_in, const int* dest, int tokens, int k, int K,
+                                     int format, uint8_t* wire_out, void* stream) {
+    if (q_in == nullptr || sf_in == nullptr || dest == nullptr || wire_out == nullptr) return DSL_ERR_NULL;
+    const size_t wb = dsl_moe_wire_bytes(K, format);
+    if (wb == 0) return format != DSL_FP4_NV && format != DSL_FP4_MX ? DSL_ERR_ENUM : DSL_ERR_SHAPE;
+    if (tokens < 0 || k < 1) return DSL_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(q_in) | reinterpret_cast<uintptr_t>(sf_in) | reinterpret_cast<uintptr_t>(wire_out)) & 15u)
+        return DSL_ERR_ALIGN;
+    const long long entries = static_cast<long long>(tokens) * k;
+    if (entries == 0) return 0;
+    if (entries > 0x7FFFFFFFll) return DSL_ERR_TOO_LARGE;
+    const int nblk = format == DSL_FP4_NV ? K / 16 : K / 32;
+    moe_pack_wire_fp4_kernel<<<static_cast<unsigned>((entries + 7) / 8), 256, 0, st_of(stream)>>>(
+        q_in, sf_in, dest, static_cast<int>(entries), k, K / 2, (nblk + 3) / 4, static_cast<int>(wb), wire_out);
+    return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dsl_moe_unpack_wire_fp4(const uint8_t* wire_in, const int* ids, const int* dest, const int* offsets,
+                                       const int* tile0, int rows, int K, int format, uint8_t* q_out, uint8_t* sf_out,
+                                       void* stream) {
+    if (wire_in == nullptr || ids == nullptr || dest == nullptr || offsets == nullptr || tile0 == nullptr || q_out == nullptr ||
+        sf_out == nullptr)
+        return DSL_ERR_NULL;
+    const size_t wb = dsl_moe_wire_bytes(K, format);
+    if (wb == 0) return format != DSL_FP4_NV && format != DSL_FP4_MX ? DSL_ERR_ENUM : DSL_ERR_SHAPE;
+    if (rows < 0) return DSL_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(wire_in) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(sf_out)) & 15u)
+        return DSL_ERR_ALIGN;
+    if (rows == 0) return 0;
+    const int nblk = format == DSL_FP4_NV ? K / 16 : K / 32;
+    moe_unpack_wire_fp4_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st_of(stream)>>>(
+        wire_in, ids, dest, offsets, tile0, rows, K / 2, (nblk + 3) / 4, static_cast<int>(wb), q_out, sf_out);
     return static_cast<int>(cudaGetLastError());
 }

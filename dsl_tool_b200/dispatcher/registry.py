@@ -36,6 +36,7 @@ def _gemm_input_schema(kernel_name: str) -> dict:
         schema["scale_a"] = "float"
         schema["scale_b"] = "float"
         schema["mode"] = "str: per_tensor | groupwise | block128 (default per_tensor)"
+        schema["group_size"] = "int: K elements per scale, a multiple of 128 (default 128; other sizes only with already-quantised operands)"
     if "fp4" in kernel_name:
         schema["scale_a"] = "Tensor uint8 (tiled block scales; packed operands only)"
         schema["scale_b"] = "Tensor uint8 (tiled block scales; packed operands only)"

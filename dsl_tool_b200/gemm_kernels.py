@@ -408,8 +408,10 @@ def fp8_gemm(A: torch.Tensor, B, scale_a: Scalar = None, scale_b: Scalar = None,
     """
     if mode not in ("per_tensor", "groupwise", "block128"):
         raise ValueError(f"mode must be per_tensor, groupwise or block128, got {mode!r}")
-    if int(group_size) != 128 and mode != "per_tensor":
-        raise ValueError("only group_size=128 is supported")
+    group_size = int(group_size)
+    if mode != "per_tensor" and (group_size < 128 or group_size % 128):
+        # the tensor cores accumulate one 128-byte stage of K before a partial product can be rescaled
+        raise ValueError(f"group_size must be a multiple of 128 (one K stage of the kernel), got {group_size}")
     if b_layout not in ("kn", "nk"):
         raise ValueError("b_layout must be 'kn' or 'nk'")
     dev = _lib.require_cuda(A, B if isinstance(B, torch.Tensor) else None)
@@ -440,10 +442,24 @@ def fp8_gemm(A: torch.Tensor, B, scale_a: Scalar = None, scale_b: Scalar = None,
                                       col_scale=col_scale)
         if not isinstance(scale_a, torch.Tensor) or not isinstance(scale_b, torch.Tensor):
             raise TypeError("group-scaled FP8 needs scale_a and scale_b tensors")
+        if group_size != 128:
+            # scales per `group_size` K-elements (cuda/gemm/fp8_gemm.cu:110-116 takes any size): each one is repeated
+            # for the 128-element groups it covers, i.e. the same products are summed in 128-element partial sums
+            rep = group_size // 128
+            ng = -(-K // group_size)
+            kg = K // 128
+            if K % 128 or scale_a.shape != (M, ng):
+                raise ValueError(f"scale_a must be [{M}, {ng}] for group_size={group_size} and K a multiple of 128")
+            scale_a = scale_a.repeat_interleave(rep, dim=1)[:, :kg].contiguous()
+            scale_b = (scale_b.repeat_interleave(rep, dim=1)[:, :kg] if mode == "block128"
+                       else scale_b.repeat_interleave(rep, dim=0)[:kg]).contiguous()
         return gemm_fp8_groupwise_quantized(A, qb, scale_a, scale_b, n=N, sb_block=(mode == "block128"),
                                             out_dtype=out_dtype, row_scale=row_scale, col_scale=col_scale)
     if A.dtype not in _FLOAT_DTYPES or B.dtype not in _FLOAT_DTYPES:
         raise TypeError(f"unsupported dtypes {A.dtype}, {B.dtype}")
+    if mode != "per_tensor" and group_size != 128:
+        raise ValueError("high-precision inputs are quantised with 1x128 groups and 128x128 blocks: pass group_size=128, "
+                         "or already-quantised operands with their own scales for a multiple of 128")
     if cache_weights and scale_b is None:
         w = cached_pack(B, "fp8" if mode == "per_tensor" else "fp8_block128", b_layout)
         if mode == "per_tensor" and scale_a is not None:

@@ -10,10 +10,17 @@ live here.  Data flow of `moe_forward` (NVFP4 weights):
       --grouped GEMM (gate/up, fused SwiGLU, result quantised in the epilogue)--> --grouped GEMM (down)-->
       --combine (weights, slot order)--> out [tokens, d_model]
 
-Expert parallelism: every rank sees all tokens and the full routing (the router is cheap), dispatches and
-computes only its contiguous range of experts (`sharding.expert_ranges`), and the per-rank partial results
-are summed with one all-reduce - there is no token all-to-all and no host-side knowledge of the row counts.
-Buffers for the routed rows are sized for the worst case of the local experts, tokens * k rows.
+Expert parallelism, two ways (`moe_forward(..., dispatch=...)`):
+  "replicated"  every rank sees all tokens and the full routing (the router is cheap), dispatches and computes only
+                its contiguous range of experts (`sharding.expert_ranges`), and the per-rank partial results are
+                summed with one all-reduce or reduce-scatter - no token exchange and no host-side knowledge of the
+                row counts.  Buffers for the routed rows are sized for the worst case, tokens * k rows.  Everything
+                outside the GEMMs is repeated on every rank, so it suits few tokens.
+  "all_to_all"  every rank owns a share of the tokens: it routes and quantises only those, sends each routed row
+                (packed e2m1 bytes + scale bytes, `dsl_moe_pack_wire_fp4`) to the rank that owns its expert with one
+                NCCL all-to-all over NVLink, multiplies what arrived, and a second all-to-all carries the results
+                back to the token's owner, which combines them.  One read-back of the per-expert row counts to the
+                host sizes the receive buffers.  Results are bit-identical to the single-GPU layer.
 """
 from __future__ import annotations
 
@@ -25,7 +32,7 @@ import torch
 from . import _lib
 from .gemm_kernels import gemm_fp4_quantized, gemm_fp8_groupwise_quantized, gemm_fp8_quantized, linear
 from .quantize import PackedWeight, pack_weight, quantize_fp4, quantize_fp8
-from .sharding import expert_ranges
+from .sharding import arrival_expert_ids, exchange_rows, expert_ranges, return_rows
 
 
 @dataclass
@@ -211,14 +218,116 @@ def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
     return combine(p, y, w.first, w.last, out_dtype=torch.float32)
 
 
+def pack_wire(p: MoEPlan, packed: torch.Tensor, sf: torch.Tensor, K: int, format: str) -> torch.Tensor:
+    """Rows quantised once per token -> one record per routed row ([tokens*k, wire bytes] uint8), expert-sorted."""
+    dev = _lib.require_cuda(packed, sf)
+    T, k = p.ids.shape
+    fmt = _lib.FP4_NV if format == "nvfp4" else _lib.FP4_MX
+    wb = int(_lib.lib().dsl_moe_wire_bytes(K, fmt))
+    wire = torch.empty((T * k, wb), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_moe_pack_wire_fp4(packed.data_ptr(), sf.data_ptr(), p.dest.data_ptr(), T, k, K, fmt, wire.data_ptr(),
+                                              _lib.stream_ptr())
+    _lib.check(rc, "dsl_moe_pack_wire_fp4")
+    return wire
+
+
+def unpack_wire(p: MoEPlan, wire: torch.Tensor, K: int, format: str):
+    """Records in arrival order (planned by `p`: one slot per record, local expert ids) -> (packed rows [rows, K/2],
+    scale tiles in the ragged-group layout): the A operand of the grouped GEMM."""
+    dev = _lib.require_cuda(wire)
+    rows = wire.shape[0]
+    fmt = _lib.FP4_NV if format == "nvfp4" else _lib.FP4_MX
+    nblk = K // 16 if format == "nvfp4" else K // 32
+    q = torch.empty((rows, K // 2), dtype=torch.uint8, device=dev)
+    sf = torch.zeros(int(_lib.lib().dsl_sf_bytes_grouped(rows, nblk, p.experts)), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dsl_moe_unpack_wire_fp4(wire.data_ptr(), p.ids.data_ptr(), p.dest.data_ptr(), p.offsets.data_ptr(),
+                                                p.tile0.data_ptr(), rows, K, fmt, q.data_ptr(), sf.data_ptr(), _lib.stream_ptr())
+    _lib.check(rc, "dsl_moe_unpack_wire_fp4")
+    return q, sf
+
+
+def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
+                           out_dtype=torch.float32, group=None) -> torch.Tensor:
+    """The layer for a rank that owns the token rows x [tokens_local, K] and the experts w.first .. w.last: returns
+    its own tokens' results [tokens_local, D].  NVFP4 / MXFP4 weights.  The NVFP4 global scale of the activations
+    is that of ALL ranks' tokens (one all-reduce of a float), so the layer computes exactly what one GPU holding
+    every token would."""
+    import torch.distributed as dist
+    fmt = w.gate_up.format
+    if fmt not in ("nvfp4", "mxfp4"):
+        raise ValueError("the all-to-all layer serves NVFP4 and MXFP4 weights")
+    dev = _lib.require_cuda(x, logits)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if (w.last - w.first) < w.experts and world == 1:
+        raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")
+    K = x.shape[1]
+    local_experts = w.last - w.first
+    ids, wts = route(logits, k, renormalize)
+    p = plan(ids, wts, w.experts)
+    gs_in = None
+    if fmt == "nvfp4":
+        amax = x.abs().amax().float().reshape(1)
+        if world > 1:
+            dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+        gs_in = torch.where(amax == 0, torch.ones_like(amax), amax / 2688.0)
+    packed, sf, gs = quantize_fp4(x, fmt, global_scale=gs_in)
+    wire = pack_wire(p, packed, sf, K, fmt)
+    counts = p.offsets[1:] - p.offsets[:-1]
+    ex = exchange_rows(wire, counts, w.experts, group)
+    R = ex.received.shape[0]
+    D = w.down.n
+    fused_hidden = fmt == "nvfp4" and w.hidden_global_scale is not None
+    h = hq = hsf = hgs = p2 = None
+    common = {}
+    if R > 0:
+        ids_in = arrival_expert_ids(ex, dev).reshape(R, 1)
+        p2 = plan(ids_in, torch.ones((R, 1), dtype=torch.float32, device=dev), local_experts)
+        q_rows, sf_rows = unpack_wire(p2, ex.received, K, fmt)
+        common = dict(format=fmt, expert_offsets=p2.offsets, b_static=True)
+        if fused_hidden:
+            hq, hsf, hgs = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
+                                              global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype="nvfp4",
+                                              out_global_scale=w.hidden_global_scale, **common)
+        else:
+            h = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
+                                   global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype=torch.bfloat16, **common)
+    if not fused_hidden:
+        # the hidden activation's global scale is that of ALL ranks' rows (every rank joins, also one without rows)
+        hgs_in = None
+        if fmt == "nvfp4":
+            amax_h = (h.abs().amax().float().reshape(1) if R > 0 else torch.zeros(1, dtype=torch.float32, device=dev))
+            if world > 1:
+                dist.all_reduce(amax_h, op=dist.ReduceOp.MAX, group=group)
+            hgs_in = torch.where(amax_h == 0, torch.ones_like(amax_h), amax_h / 2688.0)
+        if R > 0:
+            hq, hsf, hgs = quantize_fp4(h, fmt, global_scale=hgs_in, group_offsets=p2.offsets)
+    if R > 0:
+        y = gemm_fp4_quantized(hq, w.down.q, hsf, w.down.scale, n=w.down.n, global_scale_a=hgs,
+                               global_scale_b=w.down.global_scale, out_dtype=torch.bfloat16, **common)
+        y_arrival = combine(p2, y, 0, local_experts, out_dtype=torch.bfloat16)      # back to arrival order (one slot, weight 1)
+    else:
+        y_arrival = torch.empty((0, D), dtype=torch.bfloat16, device=dev)
+    back = return_rows(y_arrival, ex, group)
+    return combine(p, back, 0, w.experts, out_dtype=out_dtype)
+
+
 def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
-                out_dtype=torch.float32, group=None, reduce: str = "all_reduce", exchange_dtype=None) -> torch.Tensor:
+                out_dtype=torch.float32, group=None, reduce: str = "all_reduce", exchange_dtype=None,
+                dispatch: str = "replicated") -> torch.Tensor:
     """One MoE feed-forward layer: x [tokens, K], router logits [tokens, experts] -> [tokens, D].
+    dispatch "all_to_all": x / logits are this rank's OWN token rows and the result is theirs
+    (`moe_forward_all_to_all`); the remaining arguments below apply to "replicated".
     When `w` covers only part of the experts the per-rank partial results are summed over `group` (default: the
     default process group of torch.distributed): reduce "all_reduce" leaves the whole result on every rank,
     "reduce_scatter" leaves rank r with token rows [r * tokens / world, (r + 1) * tokens / world) - half the
     traffic, and what a sequence-sharded consumer wants.  `exchange_dtype` (e.g. torch.bfloat16) rounds the
     partial results before they travel; default fp32."""
+    if dispatch not in ("replicated", "all_to_all"):
+        raise ValueError("dispatch must be 'replicated' or 'all_to_all'")
+    if dispatch == "all_to_all":
+        return moe_forward_all_to_all(x, logits, w, k, renormalize=renormalize, out_dtype=out_dtype, group=group)
     if reduce not in ("all_reduce", "reduce_scatter"):
         raise ValueError("reduce must be 'all_reduce' or 'reduce_scatter'")
     out = moe_partial(x, logits, w, k, renormalize=renormalize)

@@ -147,6 +147,66 @@ class ExpertParallelGroupedLinear:
         return torch.cat([buf[r, :n] for r, n in enumerate(rows)], dim=0)
 
 
+# ---- token all-to-all of an expert-parallel layer (host side; kernel-free so that gloo ranks on CPU can run it) ----
+
+@dataclass
+class RowExchange:
+    """What one rank knows after the count exchange of `exchange_rows`."""
+    send_rows: List[int]            # records this rank sends to each rank (its entries for that rank's experts)
+    recv_rows: List[int]            # records it receives from each rank
+    counts_in: torch.Tensor         # [world, local experts] int32 (CPU): rows from source s for local expert e
+    received: torch.Tensor          # [sum(recv_rows), record width]: source-major, expert-sorted within a source
+
+
+def exchange_rows(records: torch.Tensor, counts_per_expert: torch.Tensor, experts: int, group=None) -> RowExchange:
+    """Sends every expert-sorted record to the rank that owns its expert.
+
+    records [entries, width] are this rank's routed rows in expert-sorted order (all `experts` global experts);
+    counts_per_expert [experts] int32 says how many belong to each.  Two collectives: the per-expert counts
+    (all-to-all of a few integers, then ONE read-back to the host, which sizes the receive buffer) and the
+    records themselves.  Both honour the process group's time limit: a rank that never joins makes them raise
+    on the others instead of hanging them.
+    """
+    rank, world = _world(group)
+    ranges = expert_ranges(experts, world)
+    first, last = ranges[rank]
+    local = last - first
+    counts_per_expert = counts_per_expert.to(torch.int32).contiguous()
+    if world == 1:
+        counts_in = counts_per_expert.cpu().view(1, local)
+        n = int(counts_in.sum())
+        return RowExchange([n], [n], counts_in, records[:n])
+    counts_in_dev = torch.empty(world * local, dtype=torch.int32, device=records.device)
+    dist.all_to_all_single(counts_in_dev, counts_per_expert, [local] * world, [l - f for f, l in ranges], group=group)
+    counts_host = counts_per_expert.cpu()
+    counts_in = counts_in_dev.cpu().view(world, local)
+    send_rows = [int(counts_host[f:l].sum()) for f, l in ranges]
+    recv_rows = [int(v) for v in counts_in.sum(dim=1)]
+    received = torch.empty((sum(recv_rows),) + tuple(records.shape[1:]), dtype=records.dtype, device=records.device)
+    dist.all_to_all_single(received, records[:sum(send_rows)].contiguous(), recv_rows, send_rows, group=group)
+    return RowExchange(send_rows, recv_rows, counts_in, received)
+
+
+def return_rows(results: torch.Tensor, ex: RowExchange, group=None) -> torch.Tensor:
+    """The way back: `results` [received rows, width] in arrival order -> this rank's own entries, in the
+    expert-sorted order it sent them in."""
+    _, world = _world(group)
+    if world == 1:
+        return results
+    back = torch.empty((sum(ex.send_rows),) + tuple(results.shape[1:]), dtype=results.dtype, device=results.device)
+    dist.all_to_all_single(back, results.contiguous(), ex.send_rows, ex.recv_rows, group=group)
+    return back
+
+
+def arrival_expert_ids(ex: RowExchange, device) -> torch.Tensor:
+    """Local expert index of every received record (int32 [received rows]): records arrive source by source,
+    expert-sorted inside a source."""
+    world, local = ex.counts_in.shape
+    experts = torch.arange(local, dtype=torch.int32).repeat(world)
+    ids = torch.repeat_interleave(experts, ex.counts_in.reshape(-1).to(torch.int64))
+    return ids.to(device)
+
+
 def shard_weight_columns(w_nk: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     """Rows [start, end) of a K-major weight [N, K] for `rank` (a view)."""
     s, e = column_ranges(w_nk.shape[0], world)[rank]

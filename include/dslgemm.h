@@ -236,6 +236,17 @@ int dsl_gemm_fp4_ref32(const uint8_t* A, const uint8_t* B, float* C, const float
  *                     [rows, K/2], sf_out in the ragged-group tile layout (zero-filled by the caller)
  *   dsl_moe_dispatch_rows the same mapping for plain rows of row_bytes (% 16 == 0) bytes
  *   dsl_moe_combine   out[t, :] = sum over t's slots with a local expert, in slot order, of weight * y[row, :]
+ *
+ * Token all-to-all (experts split over several GPUs, every GPU owning a share of the tokens): a routed row crosses
+ * the link as one record of dsl_moe_wire_bytes(K, format) bytes - the packed e2m1 bytes, then the row's scale bytes
+ * in K order (one 32-bit word per 512-byte scale tile of the row), zero-padded to a multiple of 16.
+ *   dsl_moe_pack_wire_fp4    rows quantised once per token (q_in, token-major scale tiles sf_in) -> records in the
+ *                     expert-sorted order of dest (wire_out [tokens*k, wire bytes]); contiguous runs of it go to
+ *                     the GPUs that own the experts
+ *   dsl_moe_unpack_wire_fp4  records as they arrived (record r belongs to this GPU's expert ids[r] and takes row
+ *                     dest[r] of its expert-sorted order, both from dsl_moe_plan over the arrived rows) -> packed
+ *                     rows q_out [rows, K/2] and scale tiles sf_out in the ragged-group layout (zero-filled by the
+ *                     caller), i.e. the A operand of the grouped GEMM
  */
 int dsl_moe_route(const void* logits, int dtype, int tokens, int experts, int k, int renorm, int* ids_out,
                   float* weights_out, void* stream);
@@ -250,6 +261,11 @@ int dsl_moe_dispatch_rows(const void* x, const int* ids, const int* dest, const 
 int dsl_moe_combine(const void* y, int y_dtype, const int* ids, const int* dest, const int* offsets, const float* weights,
                     int tokens, int k, int d_model, int first_expert, int last_expert, void* out, int out_dtype,
                     void* stream);
+size_t dsl_moe_wire_bytes(int K, int format);
+int dsl_moe_pack_wire_fp4(const uint8_t* q_in, const uint8_t* sf_in, const int* dest, int tokens, int k, int K, int format,
+                          uint8_t* wire_out, void* stream);
+int dsl_moe_unpack_wire_fp4(const uint8_t* wire_in, const int* ids, const int* dest, const int* offsets, const int* tile0,
+                            int rows, int K, int format, uint8_t* q_out, uint8_t* sf_out, void* stream);
 
 /*
  * dsl_gemm_fp4 for callers that cannot allocate device memory (no counterpart in the

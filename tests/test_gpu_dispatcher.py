@@ -16,7 +16,7 @@ def _spec(a: np.ndarray, dtype: str):
 
 
 def test_run_from_spec_fp8_config0(cuda_device):
-    """BASELINE config 0: fp32 N(0,1) A and B, per-tensor scale amax/448, M=N=K=1024."""
+    """The per-tensor plumbing configuration: fp32 N(0,1) A and B, per-tensor scale amax/448, M=N=K=1024."""
     from dsl_tool_b200.dispatcher import KernelDispatcher
     rng = np.random.default_rng(0)
     a = rng.standard_normal((1024, 1024)).astype(np.float32)

@@ -1,4 +1,4 @@
-"""BASELINE.json's full-size configurations on the GPU.  The oracle cannot multiply these sizes
+"""The benchmark configurations at their full sizes on the GPU.  The oracle cannot multiply these sizes
 in seconds, so the checks are (a) exact parity on a sample of output rows, whose oracle needs only
 those activation rows against the full weight, (b) bit-exact quantised bytes on the same rows, and
 (c) a closed-form case that covers every tile: constant rows times constant rows."""

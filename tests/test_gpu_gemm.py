@@ -108,6 +108,26 @@ def test_fp8_groupwise_last_round_cut_into_pieces(cuda_device, sb_block, M, N):
         assert torch.equal(got[r0:r0 + 256], alone)
 
 
+@pytest.mark.parametrize("group", [256, 384])
+def test_fp8_groupwise_wider_groups_through_the_public_callable(cuda_device, group):
+    """The reference's groupwise GEMM takes any group size (cuda/gemm/fp8_gemm.cu:110-116).  Multiples of 128 are served
+    for already-quantised operands: one scale per `group` K-elements, [M, K/group] and [K/group, N], with B in the
+    reference's [K, N] layout.  A group size below 128 (or not a multiple of it) is refused with a clear message."""
+    from dsl_tool_b200 import fp8_gemm
+    rng = np.random.default_rng(group)
+    M, N, K = 300, 520, 768
+    qa, sa = O.quant_fp8_groupwise(activations(rng, M, K), group=group)
+    w = weights(rng, N, K)
+    qb, sb_nk = O.quant_fp8_groupwise(w, group=group)            # per weight row and K group: [N, K/group]
+    sb = np.ascontiguousarray(sb_nk.T)                             # the reference's [K/group, N]
+    want = O.gemm_fp8_groupwise(qa, qb, sa, sb, group=group)
+    got = fp8_gemm(_t(qa), _t(np.ascontiguousarray(qb.T)), _t(sa), _t(sb), mode="groupwise", group_size=group)
+    _status_ok()
+    assert rel_frobenius(got.cpu().numpy(), want) <= REL_FROB_TOL
+    with pytest.raises(ValueError, match="multiple of 128"):
+        fp8_gemm(_t(qa), _t(np.ascontiguousarray(qb.T)), _t(sa), _t(sb), mode="groupwise", group_size=32)
+
+
 def test_epilogue_row_and_column_rescale(cuda_device):
     from dsl_tool_b200.gemm_kernels import gemm_fp8_quantized
     rng = np.random.default_rng(5)

@@ -165,6 +165,42 @@ def test_expert_parallel_partials_add_up(cuda_device, fmt):
         assert torch.allclose(parts[0] + parts[1], whole, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("fmt,hgs", [("nvfp4", 0.004), ("nvfp4", None), ("mxfp4", None)])
+def test_all_to_all_path_on_one_rank_equals_the_replicated_layer(cuda_device, fmt, hgs):
+    """dispatch="all_to_all" with a single rank sends nothing, but runs every kernel of that path (records packed
+    for the wire, unpacked into expert-sorted rows and scale tiles, results put back in arrival order): it must
+    give the very bits of the ordinary layer.  Shapes with an expert nobody chose and rows that do not fill tiles."""
+    rng = np.random.default_rng(60)
+    T, E, k, K, H, Dm = 333, 7, 3, 384, 128, 160
+    x, logits, w1, w2 = _layer_inputs(rng, T, E, K, H, Dm, cuda_device)
+    logits[:, 2] = -1e9
+    wts = D.MoEWeights.pack(w1, w2, fmt, hidden_global_scale=hgs)
+    base = D.moe_forward(x, logits, wts, k)
+    got = D.moe_forward(x, logits, wts, k, dispatch="all_to_all")
+    _lib.check_status()
+    assert torch.equal(got, base)
+
+
+def test_wire_records_round_trip(cuda_device):
+    """pack -> unpack of the wire records reproduces dispatch_fp4's expert-sorted rows and scale tiles bit for bit."""
+    rng = np.random.default_rng(61)
+    T, E, k, K = 300, 9, 4, 416                     # 26 scale blocks per row: the last scale tile is partly padding
+    x = torch.from_numpy(activations(rng, T, K, outliers=True)).bfloat16().to(cuda_device)
+    ids = torch.from_numpy(rng.integers(0, E, (T, k)).astype(np.int32)).to(cuda_device)
+    p = moe.plan(ids, torch.ones(T, k, device=cuda_device), E)
+    for fmt in ("nvfp4", "mxfp4"):
+        packed, sf, _ = D.quantize_fp4(x, fmt)
+        want_q, want_sf = moe.dispatch_fp4(p, packed, sf, K, fmt, 0, E)
+        wire = moe.pack_wire(p, packed, sf, K, fmt)
+        assert wire.shape == (T * k, int(_lib.lib().dsl_moe_wire_bytes(K, _lib.FP4_NV if fmt == "nvfp4" else _lib.FP4_MX)))
+        # on arrival the records are planned again, one slot each: the expert of record r is that of sorted row r
+        expert_of_row = torch.repeat_interleave(torch.arange(E, device=cuda_device, dtype=torch.int32),
+                                                (p.offsets[1:] - p.offsets[:-1]).long())
+        p2 = moe.plan(expert_of_row.reshape(-1, 1).contiguous(), torch.ones(T * k, 1, device=cuda_device), E)
+        q, sf2 = moe.unpack_wire(p2, wire, K, fmt)
+        assert torch.equal(q, want_q) and torch.equal(sf2, want_sf)
+
+
 def test_token_permutation_invariance_at_scale(cuda_device):
     """Size-independent property of the whole layer: permuting the tokens permutes the result rows and changes
     nothing else (a row's value depends only on the token, its experts and the fixed summation orders)."""

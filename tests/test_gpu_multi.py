@@ -61,6 +61,24 @@ for fmt in ("nvfp4", "bf16"):
     err = float((shard - ref).norm() / ref.norm())
     print(rank, fmt, "moe layer reduce-scatter (bf16 exchange) relF", err, tuple(shard.shape), flush=True)
     ok &= err < 1e-2 and tuple(shard.shape) == (rows, D)
+# token all-to-all: every rank owns half of the tokens and half of the experts; bit-identical to one GPU holding all
+for fmt, hgs in (("nvfp4", 0.004), ("nvfp4", None), ("mxfp4", None)):
+    whole = moe_forward(xm, lg, MoEWeights.pack(w1, w2, fmt, hidden_global_scale=hgs), k)
+    rows = T // world
+    mine = slice(rank * rows, (rank + 1) * rows)
+    got = moe_forward(xm[mine].contiguous(), lg[mine].contiguous(),
+                      MoEWeights.pack(w1, w2, fmt, rank=rank, world=world, hidden_global_scale=hgs), k, dispatch="all_to_all")
+    same = bool(torch.equal(got, whole[mine]))
+    print(rank, fmt, hgs, "moe layer token all-to-all identical", same, tuple(got.shape), flush=True)
+    ok &= same
+# a rank that receives nothing: every token prefers the experts of rank 0
+lg0 = lg.clone(); lg0[:, E // 2:] = -1e9
+whole = moe_forward(xm, lg0, MoEWeights.pack(w1, w2, "nvfp4", hidden_global_scale=None), k)
+got = moe_forward(xm[mine].contiguous(), lg0[mine].contiguous(), MoEWeights.pack(w1, w2, "nvfp4", rank=rank, world=world), k,
+                  dispatch="all_to_all")
+same = bool(torch.equal(got, whole[mine]))
+print(rank, "all-to-all with an idle rank identical", same, flush=True)
+ok &= same
 torch.cuda.synchronize()
 dist.destroy_process_group()
 sys.exit(0 if ok else 3)

@@ -91,3 +91,79 @@ def test_two_rank_split_and_gather():
         p.join(120)
         assert p.exitcode == 0
     assert dict(results) == {0: True, 1: True}
+
+
+# ---- token all-to-all (host side) and what happens when a rank stops taking part -------------------------------
+
+def _exchange_worker(rank, world, port, results):
+    from dsl_tool_b200.sharding import arrival_expert_ids, exchange_rows, return_rows
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        E = 5                                                     # experts 0-2 on rank 0, 3-4 on rank 1
+        counts = torch.tensor([[3, 0, 2, 4, 1], [0, 0, 5, 0, 2]][rank], dtype=torch.int32)   # expert 1 gets nothing at all
+        n = int(counts.sum())
+        expert_of = torch.repeat_interleave(torch.arange(E), counts.long())
+        # a record says who sent it, for which expert, and its position in the sender's sorted order
+        records = torch.stack([torch.full((n,), rank), expert_of, torch.arange(n)], dim=1).to(torch.int32)
+        ex = exchange_rows(records, counts, E, None)
+        first = [0, 3][rank]
+        ids = arrival_expert_ids(ex, "cpu")
+        ok = bool((ex.received[:, 1] - first == ids).all())       # every arrived record belongs to the expert the counts say
+        ok &= ex.recv_rows == [int(((ex.received[:, 0] == s)).sum()) for s in range(world)]
+        ok &= sorted(ex.received[ex.received[:, 0] == 0][:, 2].tolist()) == ex.received[ex.received[:, 0] == 0][:, 2].tolist()
+        back = return_rows(ex.received * 10, ex, None)            # "compute" = times ten, then the way back
+        ok &= bool(torch.equal(back, records * 10))
+        results[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_token_exchange_round_trip():
+    port = _free_port()
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_exchange_worker, args=(2, port, results), nprocs=2, join=True)
+    assert results[0] and results[1]
+
+
+def _leaving_worker(rank, world, port, results, what):
+    import datetime
+    import time
+    from dsl_tool_b200.sharding import all_gather_columns, column_ranges, exchange_rows
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    store = dist.distributed_c10d._get_default_store()
+
+    def step():
+        if what == "gather":
+            return all_gather_columns(torch.full((3, 128), float(rank)), column_ranges(256, world), None)
+        counts = torch.tensor([2, 1], dtype=torch.int32)
+        return exchange_rows(torch.arange(6, dtype=torch.int32).reshape(3, 2), counts, 2, None)
+
+    step()                                                        # step 1: everybody takes part
+    if rank == 1:
+        # leaves BETWEEN two steps (nothing of its own is in flight) and stays away until rank 0 has seen the failure
+        store.wait(["rank0_saw_it"], datetime.timedelta(seconds=60))
+        results[rank] = "left"
+        return                                                    # no destroy_process_group: the group is broken by design
+    t0 = time.monotonic()
+    try:
+        step()                                                    # step 2: the peer never joins
+        results[rank] = "no error"
+    except Exception as exc:                                      # the group's time limit (or the transport) ends the wait
+        results[rank] = f"raised after {time.monotonic() - t0:.1f}s: {type(exc).__name__}"
+    store.set("rank0_saw_it", "1")
+
+
+@pytest.mark.parametrize("what", ["gather", "exchange"])
+def test_a_rank_that_stops_taking_part_ends_the_collective_with_an_error(what):
+    """The all-gather of the column shards and the token exchange are host-launched collectives: when a rank does not
+    join, the others must come back with an exception within the process group's time limit instead of hanging."""
+    port = _free_port()
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_leaving_worker, args=(2, port, results, what), nprocs=2, join=True)
+    assert results[1] == "left"
+    assert results[0].startswith("raised after"), results[0]
+    assert float(results[0].split()[2].rstrip("s:")) < 30.0
