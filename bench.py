@@ -49,6 +49,8 @@ WORKLOADS = {
     "fp8_per_tensor_1024": dict(kind="fp8", M=1024, K=1024, N=1024, wstd=1.0, outliers=False),
     "fp8_groupwise_8192": dict(kind="fp8_block128", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
     "nvfp4_8192": dict(kind="nvfp4", M=8192, K=8192, N=8192, wstd=0.02, outliers=True),
+    # the same with a calibrated (static) global scale of the activations: the quantiser is one pass over them
+    "nvfp4_8192_static_scale": dict(kind="nvfp4", M=8192, K=8192, N=8192, wstd=0.02, outliers=True, act_gs=20.0 / 2688.0),
     "nvfp4_m1024": dict(kind="nvfp4", M=1024, K=8192, N=8192, wstd=0.02, outliers=True),
     "nvfp4_m128": dict(kind="nvfp4", M=128, K=8192, N=8192, wstd=0.02, outliers=True),
     "nvfp4_m16": dict(kind="nvfp4", M=16, K=8192, N=8192, wstd=0.02, outliers=True),
@@ -77,7 +79,7 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "fp8_groupwise_llama8b_mlp"
 # further configurations reported in `sweep` (one GPU) ...
-SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_m1", "nvfp4_m16", "nvfp4_m128", "nvfp4_m1024",
+SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_8192_static_scale", "nvfp4_m1", "nvfp4_m16", "nvfp4_m128", "nvfp4_m1024",
               "mxfp4_llama70b_up", "mxfp4_llama70b_down", "moe_nvfp4", "moe_nvfp4_tokens", "moe_nvfp4_skewed",
               "moe_fp8_groupwise", "moe_layer_nvfp4"]
 # ... and the sharded ones when the problem is split over several GPUs
@@ -236,10 +238,10 @@ def build_workload(name, rank, world, device, sets, strong=False):
             return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype="nvfp4", out_global_scale=1.0 / 2688.0,
                           expert_offsets=offs, activation=cfg.get("act"))[0]
         return linear(acts[i % sets] if a is None else a, wts[i % sets], out_dtype=torch.bfloat16, expert_offsets=offs,
-                      activation=cfg.get("act"))
+                      activation=cfg.get("act"), act_global_scale=cfg.get("act_gs"))
 
     return dict(step=step, acts=acts, wts=wts, offs=offs, M=M, K=K, N=N, kind=kind, flops=2.0 * M * N * K,
-                moe=bool(cfg.get("moe")), act=cfg.get("act"), out=cfg.get("out"))
+                moe=bool(cfg.get("moe")), act=cfg.get("act"), out=cfg.get("out"), act_gs=cfg.get("act_gs"))
 
 
 def build_layer_workload(cfg, rank, world, device, sets, strong, g):
@@ -321,7 +323,7 @@ def split_step(wl):
         if kind == "fp8_block128":
             return quantize_fp8(a, "groupwise")
         if kind in ("nvfp4", "mxfp4"):
-            return quantize_fp4(a, kind, group_offsets=offs)
+            return quantize_fp4(a, kind, global_scale=wl.get("act_gs"), group_offsets=offs)
         return (a,)
 
     def gemm(i, q):

@@ -17,7 +17,8 @@
 // element is unchanged, so the result is bit-identical to the uncut schedule.
 //
 //   warp 0     TMA producer          warp 1   leader: MMA issuer / peer: "stage landed" forwarder
-//   warps 2-9  promotion + epilogue: warp w owns lanes 32*(w%4).. and 128 of the 256 columns (32 of a piece's 64)
+//   warps 2-17 promotion + epilogue: warp w owns lanes 32*(w%4).. and 64 of the 256 columns (the first eight of them
+//              also 32 of a piece's 64)
 #include <cuda_bf16.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -43,7 +44,14 @@ constexpr int NUM_BARS = 3 * NUM_STAGES + 4 + 2 * NARROW_RING;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
 constexpr int OFF_TABLE = OFF_MISC + 16;
 constexpr int SMEM_BYTES = OFF_TABLE + 2 * (DSL_MAX_GROUPS + 1) * 4 + 1024;
-constexpr int THREADS = 320;
+// Promotion warps per CTA: 4 lane quarters x PARTS column parts.  The promotion is bound by the latency of its
+// tensor-memory loads (a warp can only wait for ALL of its outstanding loads), so what hides that latency is warps.
+#ifndef DSL_GWP_PARTS
+#define DSL_GWP_PARTS 4
+#endif
+constexpr int PARTS = DSL_GWP_PARTS;            // 2: 8 warps x 128 columns, 4: 16 warps x 64 columns
+constexpr int PROMO_WARPS = 4 * PARTS;
+constexpr int THREADS = 64 + 32 * PROMO_WARPS;
 static_assert(SMEM_BYTES > 116224 && SMEM_BYTES <= 232448, "one CTA per SM");
 
 constexpr int NARROW_N = 64;                 // width of the pieces a last-round tile is cut into
@@ -101,13 +109,23 @@ struct Walker {
 
 }  // namespace gwp
 
-// One tile of the promotion warps' work: PIECES 16-column pieces of this warp's half of the tile, K group by K group.
-// A warp's share is PIECES * 16 adjacent columns, half 1 starting right after half 0's.  The partial products arrive in a
-// ring of RING tensor-memory buffers PIECES * 32 columns apart; `step` counts the K groups this ring has carried.
-template <bool SB_BLOCK, bool ACT, int PIECES, int RING>
+// One tile of the promotion warps' work: PIECES 16-column pieces of this warp's part of the tile, K group by K group.
+// A warp's share is PIECES * 16 adjacent columns, part p starting right after part p - 1's.  The partial products arrive
+// in a ring of RING tensor-memory buffers `buf_cols` columns apart; `step` counts the K groups this ring has carried.
+// acc = p * s + acc on two adjacent columns with one packed instruction (fma.rn.f32x2: two IEEE fused multiply-adds,
+// the same bits as two fmaf calls)
+__device__ __forceinline__ void fma_pair(float& a0, float& a1, uint32_t p0, uint32_t p1, unsigned long long s2) {
+    unsigned long long a, p;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "r"(p0), "r"(p1));
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(a) : "l"(p), "l"(s2));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(a));
+}
+
+template <bool SB_BLOCK, bool ACT, int PIECES, int RING, bool FMA2 = true>
 __device__ __forceinline__ bool promote_tile(const GemmArgs& args, const gwp::Tile& ti, int num_kb, int nb128, uint32_t tmem_base,
                                              uint64_t* part_full, uint64_t* part_empty, volatile uint32_t* abort_flag,
-                                             uint32_t& step, int rank, int quad, int half, int lane) {
+                                             uint32_t& step, int rank, int quad, int half, int lane, int buf_cols) {
     using namespace gwp;
     const int row = ti.row0 + 128 * rank + quad * 32 + lane;
     const bool row_ok = row < ti.row_end;
@@ -136,7 +154,7 @@ __device__ __forceinline__ bool promote_tile(const GemmArgs& args, const gwp::Ti
         const uint32_t pphase = (step / RING) & 1u;
         if (!mbar_wait_cluster(part_full + p, pphase, abort_flag, ST_TIMEOUT_EPILOGUE)) return false;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + p * (PIECES * 32) + half * (PIECES * 16) + (static_cast<uint32_t>(quad * 32) << 16);
+        const uint32_t taddr = tmem_base + p * buf_cols + half * (PIECES * 16) + (static_cast<uint32_t>(quad * 32) << 16);
         uint32_t buf[2][16];
         tmem_ld_32x32b_x16(taddr, buf[0]);
 #pragma unroll
@@ -149,7 +167,13 @@ __device__ __forceinline__ bool promote_tile(const GemmArgs& args, const gwp::Ti
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(part_empty + p, 0);
             }
-            if (SB_BLOCK) {
+            if (SB_BLOCK && FMA2) {
+                unsigned long long s2;
+                asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "f"(s));
+#pragma unroll
+                for (int i = 0; i < 16; i += 2)
+                    fma_pair(acc[c * 16 + i], acc[c * 16 + i + 1], buf[c & 1][i], buf[c & 1][i + 1], s2);
+            } else if (SB_BLOCK) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
                     acc[c * 16 + i] = fmaf(__uint_as_float(buf[c & 1][i]), s, acc[c * 16 + i]);
@@ -182,7 +206,7 @@ __device__ __forceinline__ bool promote_tile(const GemmArgs& args, const gwp::Ti
     return true;
 }
 
-template <bool SB_BLOCK, bool ACT>
+template <bool SB_BLOCK, bool ACT, bool FMA2 = true>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gwp::THREADS, 1)
 gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                                const __grid_constant__ CUtensorMap tmap_b_narrow, const GemmArgs args) {
@@ -214,7 +238,7 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             mbar_init(peer_full + i, 1);
             mbar_init(empty_bar + i, 1);
         }
-        for (int i = 0; i < 2; ++i) { mbar_init(part_full + i, 1); mbar_init(part_empty + i, 16); }
+        for (int i = 0; i < 2; ++i) { mbar_init(part_full + i, 1); mbar_init(part_empty + i, 2 * PROMO_WARPS); }
         for (int i = 0; i < NARROW_RING; ++i) { mbar_init(nar_full + i, 1); mbar_init(nar_empty + i, 16); }
         *abort_flag = 0;
         fence_mbar_init();
@@ -346,20 +370,21 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     } else {
         // ================= promotion + epilogue =================
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int part = (warp - 2) >> 2;
         const int nb128 = (args.n + 127) / 128;
         uint32_t step = 0;
         bool ok = true;
         for (int t = pair_id; t < tw.items && ok; t += num_pairs) {
             const Tile ti = tw.decode(t);
-            // full width: 128 columns per warp, two buffers; a 64-column piece (a pair's last item): 32 per warp, its own ring
+            // full width: TILE_N / PARTS columns per warp, two buffers; a 64-column piece (a pair's last item) goes to the
+            // warps of the first two parts, 32 columns each, through its own ring
             if (ti.width == TILE_N) {
-                ok = promote_tile<SB_BLOCK, ACT, TILE_N / 32, 2>(args, ti, num_kb, nb128, tmem_base, part_full, part_empty, abort_flag,
-                                                                 step, static_cast<int>(rank), quad, half, lane);
-            } else {
+                ok = promote_tile<SB_BLOCK, ACT, TILE_N / (16 * PARTS), 2, FMA2>(args, ti, num_kb, nb128, tmem_base, part_full, part_empty,
+                                                                                 abort_flag, step, static_cast<int>(rank), quad, part, lane, TILE_N);
+            } else if (part < 2) {
                 uint32_t nstep = 0;
-                ok = promote_tile<SB_BLOCK, ACT, NARROW_N / 32, NARROW_RING>(args, ti, num_kb, nb128, tmem_base, nar_full, nar_empty,
-                                                                             abort_flag, nstep, static_cast<int>(rank), quad, half, lane);
+                ok = promote_tile<SB_BLOCK, ACT, NARROW_N / 32, NARROW_RING, FMA2>(args, ti, num_kb, nb128, tmem_base, nar_full, nar_empty,
+                                                                             abort_flag, nstep, static_cast<int>(rank), quad, part, lane, NARROW_N);
             }
         }
     }
@@ -380,7 +405,7 @@ gemm_fp8_groupwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     }
 }
 
-template <bool SB_BLOCK, bool ACT>
+template <bool SB_BLOCK, bool ACT, bool FMA2 = true>
 static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cudaStream_t st) {
     CUtensorMap ta, tb, tbn;
     const int groups = args.group_offsets != nullptr ? args.num_groups : 1;
@@ -392,7 +417,7 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     if (dev < 0) return static_cast<int>(cudaErrorInvalidDevice);
     int max_clusters = clusters_of.v[dev].load(std::memory_order_acquire);
     if (max_clusters == 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT, FMA2>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, gwp::SMEM_BYTES);
         if (e != cudaSuccess) return static_cast<int>(e);
         const int sms = sm_count();
@@ -401,7 +426,7 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
         cfg.blockDim = dim3(gwp::THREADS);
         cfg.dynamicSmemBytes = gwp::SMEM_BYTES;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT, FMA2>, &cfg);
         max_clusters = (e == cudaSuccess && n > 0) ? n : (sms > 1 ? sms / 2 : 1);
         (void)cudaGetLastError();
         clusters_of.v[dev].store(max_clusters, std::memory_order_release);
@@ -425,7 +450,7 @@ static int launch_gw_pair(const void* A, const void* B, const GemmArgs& args, cu
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT>, ta, tb, tbn, args));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_fp8_groupwise_pair_kernel<SB_BLOCK, ACT, FMA2>, ta, tb, tbn, args));
 }
 
 // The kernel's work list, computed on the host with the kernel's own Walker (no CUDA call): item i of the launch goes
@@ -478,6 +503,10 @@ int launch_gemm_fp8_groupwise_pair(const void* A, const void* B, GemmArgs args, 
     // two instantiations: the plain epilogue keeps the promotion loop free of spills, the activation one is larger
     if (args.act != DSL_ACT_NONE)
         return args.sb_block ? launch_gw_pair<true, true>(A, B, args, st) : launch_gw_pair<false, true>(A, B, args, st);
+    // block scales: the promotion multiplies two columns per instruction (fma.rn.f32x2: 1864 -> 1929 TFLOP/s cool,
+    // 1544 -> 1590 at the power cap on 4096 x 4096 x 14336); DSLGEMM_GW_FMA2=0 selects the scalar form (measurements)
+    static const bool scalar_fma = [] { const char* e = getenv("DSLGEMM_GW_FMA2"); return e != nullptr && e[0] == '0'; }();
+    if (args.sb_block && scalar_fma) return launch_gw_pair<true, false, false>(A, B, args, st);
     return args.sb_block ? launch_gw_pair<true, false>(A, B, args, st) : launch_gw_pair<false, false>(A, B, args, st);
 }
 

@@ -132,12 +132,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
     }
-    load_group_offsets(s_offs, args.group_offsets, groups, args.m_total);
     if (C::SF_ATOMS > 0) {
         uint32_t* z = reinterpret_cast<uint32_t*>(smem + C::OFF_SFA);
         for (int i = threadIdx.x; i < C::NUM_STAGES * (C::SFA_STAGE + C::SFB_STAGE) / 4; i += blockDim.x) z[i] = 0u;
         fence_proxy_async_smem();
     }
+    __syncthreads();
+    cluster_sync_all();   // both CTAs' barriers exist before anything can signal them
+    if (warp == 1) tmem_alloc_pair(tmem_ptr, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    // Everything above touches no global memory, so under programmatic stream serialisation it runs while the
+    // preceding kernel of the stream (the activation quantiser) drains; from here on that kernel's results are
+    // read (the row-group table first, then operands and scales).
+    griddep_wait();
+    load_group_offsets(s_offs, args.group_offsets, groups, args.m_total);
     __syncthreads();
     if (threadIdx.x == 0) {
         int t = 0, st = 0;
@@ -154,13 +167,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         s_sft0[groups] = st;
     }
     __syncthreads();
-    cluster_sync_all();   // both CTAs' barriers exist before anything can signal them
-    if (warp == 1) tmem_alloc_pair(tmem_ptr, TMEM_COLS);
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_ptr;
 
     pr::PairWalker tw;
     tw.offs = s_offs;
@@ -404,8 +410,21 @@ static int launch_pair_one(const void* A, const void* B, const GemmArgs& args, l
     }
     long long clusters = max_tiles < max_clusters ? max_tiles : max_clusters;
     if (clusters < 1) clusters = 1;
-    gemm_pair_kernel<KIND><<<static_cast<unsigned>(2 * clusters), 192, C::SMEM_BYTES, st>>>(ta, tb, args);
-    return static_cast<int>(cudaGetLastError());
+    // Launched with programmatic stream serialisation: the grid's set-up (barriers, tensor-memory allocation)
+    // overlaps the tail of the preceding kernel of the stream when that kernel allows it (the quantisers do);
+    // the kernel's griddep_wait() guards every read of global memory.  DSLGEMM_PDL=0 launches it the plain way.
+    static const bool pdl = [] { const char* e = getenv("DSLGEMM_PDL"); return !(e != nullptr && e[0] == '0'); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<KIND>, ta, tb, args));
 }
 
 int launch_gemm_pair(int kind, const void* A, const void* B, GemmArgs args, cudaStream_t st) {

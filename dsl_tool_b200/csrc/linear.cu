@@ -96,10 +96,15 @@ extern "C" int dsl_linear(const void* x, int x_dtype, long long M, const dsl_wei
             if (w->scale == nullptr) return DSL_ERR_NULL;
             const int fmt = w->format == DSL_W_NVFP4 ? DSL_FP4_NV : DSL_FP4_MX;
             if (fmt == DSL_FP4_NV && w->global_scale == nullptr) return DSL_ERR_NULL;
-            rc = dsl_quant_fp4(x, x_dtype, M, w->k, fmt, gs, 0, qa, static_cast<uint8_t*>(scales), offs, w->groups, ws, stream);
+            // NVFP4: a global scale handed in through ep->scale_a_dev (calibrated, or known from the producer of x)
+            // is used as it is, which makes the quantiser ONE pass over x; otherwise it comes from an amax pass
+            const bool gs_given = fmt == DSL_FP4_NV && ep->scale_a_dev != nullptr;
+            float* gs_io = gs_given ? const_cast<float*>(ep->scale_a_dev) : gs;
+            rc = dsl_quant_fp4(x, x_dtype, M, w->k, fmt, gs_io, gs_given ? 1 : 0, qa, static_cast<uint8_t*>(scales), offs, w->groups,
+                               ws, stream);
             if (rc != 0) return rc;
             if (fmt == DSL_FP4_NV) {
-                e.scale_a_dev = gs;
+                e.scale_a_dev = gs_io;
                 e.scale_b_dev = w->global_scale;
             } else {
                 e.scale_a_dev = e.scale_b_dev = nullptr;

@@ -287,7 +287,7 @@ def _weight_desc(w: PackedWeight) -> "_lib.Weight":
 
 
 def _linear_one_call(a: torch.Tensor, w: PackedWeight, out_dtype, offs: Optional[torch.Tensor], row_scale, col_scale,
-                     activation: Optional[str], out_global_scale: Scalar):
+                     activation: Optional[str], out_global_scale: Scalar, act_global_scale: Scalar = None):
     """Quantise + GEMM through the single C entry point `dsl_linear`: one call into the library, the quantised
     activations in a per-stream arena instead of fresh allocations."""
     dev = a.device
@@ -306,6 +306,13 @@ def _linear_one_call(a: torch.Tensor, w: PackedWeight, out_dtype, offs: Optional
     if col_scale is not None:
         col_scale = col_scale.detach().to(device=dev, dtype=torch.float32).contiguous()
         ep.col_scale = col_scale.data_ptr()
+    if act_global_scale is not None:
+        if w.format != "nvfp4":
+            raise ValueError("act_global_scale applies to NVFP4 weights")
+        ags = (act_global_scale.detach().to(device=dev, dtype=torch.float32).reshape(1) if isinstance(act_global_scale, torch.Tensor)
+               else torch.full((1,), float(act_global_scale), dtype=torch.float32, device=dev))
+        keep.append(ags)
+        ep.scale_a_dev = ags.data_ptr()
     switch = torch.cuda.current_device() != dev.index
     if switch:
         prev = torch.cuda.current_device()
@@ -338,7 +345,7 @@ def _linear_one_call(a: torch.Tensor, w: PackedWeight, out_dtype, offs: Optional
 
 def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
            expert_offsets: Optional[torch.Tensor] = None, row_scale=None, col_scale=None,
-           activation: Optional[str] = None, out_global_scale: Scalar = None):
+           activation: Optional[str] = None, out_global_scale: Scalar = None, act_global_scale: Scalar = None):
     """a [M, K] high-precision activations x packed weight -> [M, N]: quantise the activations
     in the weight's format (one pass on the GPU) and run the matching GEMM.  The packed weight is
     treated as complete (the activation quantiser always sits between its producer and the GEMM).
@@ -346,7 +353,9 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
     the result is [M, N/2] = silu(gate) * up (gelu(gate) * up, tanh form), computed in the GEMM epilogue
     (cuda/activations/fused_gated_activations.cu:75-90 without the [M, N] round trip through memory).
     out_dtype "nvfp4" (with `out_global_scale`): the result is quantised in the same epilogue and returned as
-    (packed bytes, scale tiles, global scale), the A operand of a following `gemm_fp4_quantized`."""
+    (packed bytes, scale tiles, global scale), the A operand of a following `gemm_fp4_quantized`.
+    `act_global_scale` (NVFP4 weights): the fp32 global scale of the activations, a float or a device scalar - a
+    calibrated value instead of amax(a) / 2688.  The quantiser then reads `a` once instead of twice (no amax pass)."""
     if _activation_code(activation) != _lib.ACT_NONE and not w.gate_up_interleaved:
         raise ValueError("a gated activation needs a weight packed with gate_up_interleave=True")
     if a.dim() != 2 or a.shape[1] != w.k:
@@ -362,7 +371,9 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
             offs, groups = _offsets_arg(expert_offsets, a.device)
             if groups != w.groups:
                 raise ValueError(f"expert_offsets describes {groups} groups, the weight holds {w.groups}")
-        return _linear_one_call(a, w, out_dtype, offs, row_scale, col_scale, activation, out_global_scale)
+        return _linear_one_call(a, w, out_dtype, offs, row_scale, col_scale, activation, out_global_scale, act_global_scale)
+    if act_global_scale is not None and w.format != "nvfp4":
+        raise ValueError("act_global_scale applies to NVFP4 weights")
     common = dict(n=w.n, out_dtype=out_dtype, expert_offsets=expert_offsets, activation=activation)
     if _is_nvfp4_out(out_dtype):
         common["out_global_scale"] = out_global_scale
@@ -376,7 +387,8 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
         return gemm_fp8_groupwise_quantized(qa, w.q, sa, w.scale, sb_block=True, row_scale=row_scale,
                                             col_scale=col_scale, **common)
     if w.format in ("nvfp4", "mxfp4"):
-        pa, sfa, gsa = quantize_fp4(a, w.format, group_offsets=expert_offsets)
+        pa, sfa, gsa = quantize_fp4(a, w.format, global_scale=act_global_scale if w.format == "nvfp4" else None,
+                                    group_offsets=expert_offsets)
         return gemm_fp4_quantized(pa, w.q, sfa, w.scale, format=w.format, global_scale_a=gsa,
                                   global_scale_b=w.global_scale, row_scale=row_scale, col_scale=col_scale, b_static=True,
                                   **common)

@@ -248,6 +248,13 @@ def unpack_wire(p: MoEPlan, wire: torch.Tensor, K: int, format: str):
     return q, sf
 
 
+def _global_scale_of(amax: torch.Tensor) -> torch.Tensor:
+    """amax / 2688 as the quantiser computes it (one IEEE division; an all-zero tensor gets 1).  Tensor by tensor:
+    dividing by a Python number may be turned into a multiplication by its reciprocal, which rounds differently."""
+    gs = torch.div(amax, torch.full_like(amax, 2688.0))
+    return torch.where(amax == 0, torch.ones_like(amax), gs)
+
+
 def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
                            out_dtype=torch.float32, group=None) -> torch.Tensor:
     """The layer for a rank that owns the token rows x [tokens_local, K] and the experts w.first .. w.last: returns
@@ -267,11 +274,10 @@ def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights,
     ids, wts = route(logits, k, renormalize)
     p = plan(ids, wts, w.experts)
     gs_in = None
-    if fmt == "nvfp4":
+    if fmt == "nvfp4" and world > 1:
         amax = x.abs().amax().float().reshape(1)
-        if world > 1:
-            dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
-        gs_in = torch.where(amax == 0, torch.ones_like(amax), amax / 2688.0)
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+        gs_in = _global_scale_of(amax)
     packed, sf, gs = quantize_fp4(x, fmt, global_scale=gs_in)
     wire = pack_wire(p, packed, sf, K, fmt)
     counts = p.offsets[1:] - p.offsets[:-1]
@@ -296,11 +302,10 @@ def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights,
     if not fused_hidden:
         # the hidden activation's global scale is that of ALL ranks' rows (every rank joins, also one without rows)
         hgs_in = None
-        if fmt == "nvfp4":
+        if fmt == "nvfp4" and world > 1:
             amax_h = (h.abs().amax().float().reshape(1) if R > 0 else torch.zeros(1, dtype=torch.float32, device=dev))
-            if world > 1:
-                dist.all_reduce(amax_h, op=dist.ReduceOp.MAX, group=group)
-            hgs_in = torch.where(amax_h == 0, torch.ones_like(amax_h), amax_h / 2688.0)
+            dist.all_reduce(amax_h, op=dist.ReduceOp.MAX, group=group)
+            hgs_in = _global_scale_of(amax_h)
         if R > 0:
             hq, hsf, hgs = quantize_fp4(h, fmt, global_scale=hgs_in, group_offsets=p2.offsets)
     if R > 0:

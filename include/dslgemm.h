@@ -194,7 +194,9 @@ int dsl_gemm_fp4(const uint8_t* A, const uint8_t* B, const uint8_t* sfa, const u
  *                call consumes it, so calls issued in order on one stream may share one area.  Calls that can
  *                overlap on the GPU (different streams) need separate areas, like dsl_epilogue.workspace.
  *   ep           as for dsl_gemm_*; scale_a / scale_b are filled in here (activation scale, weight scale) and
- *                b_is_static is set.
+ *                b_is_static is set.  NVFP4 only: a non-NULL ep->scale_a_dev on entry is taken as the activations'
+ *                global scale (a calibrated value, device float); the quantiser then needs no amax pass and reads
+ *                x once.  Otherwise the global scale is amax(x) / 2688, which costs a pass of its own.
  */
 enum { DSL_W_FP8 = 0, DSL_W_FP8_BLOCK128 = 1, DSL_W_NVFP4 = 2, DSL_W_MXFP4 = 3, DSL_W_BF16 = 4 };
 typedef struct {

@@ -128,6 +128,27 @@ def test_fp8_groupwise_wider_groups_through_the_public_callable(cuda_device, gro
         fp8_gemm(_t(qa), _t(np.ascontiguousarray(qb.T)), _t(sa), _t(sb), mode="groupwise", group_size=32)
 
 
+@pytest.mark.parametrize("gs", [20.0 / 2688.0, 3.0 / 2688.0])
+def test_nvfp4_calibrated_activation_scale_is_one_pass_and_exact(cuda_device, gs):
+    """`linear(..., act_global_scale=gs)`: the activations are quantised with the given global scale (no amax pass);
+    bytes and product equal the oracle's with that scale - also when it is too small and values saturate."""
+    from dsl_tool_b200 import pack_weight, quantize_fp4
+    from dsl_tool_b200.gemm_kernels import linear
+    rng = np.random.default_rng(91)
+    M, N, K = 260, 384, 512
+    a = torch.from_numpy(activations(rng, M, K, outliers=True)).bfloat16()
+    w = torch.from_numpy(weights(rng, N, K)).bfloat16()
+    pw = pack_weight(w.cuda(), "nvfp4")
+    got = linear(a.cuda(), pw, out_dtype="float32", act_global_scale=gs)
+    _status_ok()
+    pa, sfa, gsa = O.quant_nvfp4(a.float().numpy(), global_scale=np.float32(gs))
+    pb, sfb, gsb = O.quant_nvfp4(w.float().numpy())
+    assert rel_frobenius(got.cpu().numpy(), O.gemm_nvfp4(pa, sfa, gsa, pb, sfb, gsb)) <= REL_FROB_TOL
+    q, _, g = quantize_fp4(a.cuda(), "nvfp4", global_scale=gs)
+    assert (q.cpu().numpy() == pa).all() and g.item() == np.float32(gs)
+    assert torch.equal(got, linear(a.cuda(), pw, out_dtype="float32", act_global_scale=torch.tensor([gs], device="cuda")))
+
+
 def test_epilogue_row_and_column_rescale(cuda_device):
     from dsl_tool_b200.gemm_kernels import gemm_fp8_quantized
     rng = np.random.default_rng(5)
