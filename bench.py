@@ -75,6 +75,9 @@ WORKLOADS = {
     # gate/up GEMM with SwiGLU and NVFP4 result, down GEMM, combine); 0.01 = calibrated hidden global scale
     "moe_layer_nvfp4": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
                             hidden_gs=0.01),
+    # the same layer with the tokens split over the ranks and a token all-to-all either side of the expert GEMMs
+    "moe_layer_nvfp4_a2a": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
+                                hidden_gs=0.01, a2a=True),
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
 }
 DEFAULT_WORKLOAD = "fp8_groupwise_llama8b_mlp"
@@ -84,7 +87,7 @@ SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_
               "moe_fp8_groupwise", "moe_layer_nvfp4"]
 # ... and the sharded ones when the problem is split over several GPUs
 SWEEP_SHARDED = ["mxfp4_llama70b_up", "mxfp4_llama70b_up_gather", "mxfp4_llama70b_down", "moe_nvfp4", "moe_fp8_groupwise",
-                 "moe_layer_nvfp4"]
+                 "moe_layer_nvfp4", "moe_layer_nvfp4_a2a"]
 DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
 # dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from ncu captures of the
 # full-size workloads: bytes.  None where no capture exists.
@@ -249,11 +252,13 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
     scaling: the experts of one layer are split over the ranks, tokens replicated, partial results reduce-scattered."""
     from dsl_tool_b200 import MoEWeights, moe_forward
     T, E, k, K, H, D = cfg["tokens"], cfg["experts"], cfg["topk"], cfg["K"], cfg["H"], cfg["D"]
+    a2a = bool(cfg.get("a2a")) and strong and world > 1
+    mine = slice(rank * (T // world), (rank + 1) * (T // world)) if a2a else slice(0, T)
     acts, logits, wts = [], [], []
     for s in range(sets):
         gen = torch.Generator(device=device).manual_seed(77 + s + (0 if strong else 1000 * rank))
-        acts.append(torch.randn((T, K), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16))
-        logits.append(torch.randn((T, E), generator=gen, device=device, dtype=torch.float32))
+        acts.append(torch.randn((T, K), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)[mine].contiguous())
+        logits.append(torch.randn((T, E), generator=gen, device=device, dtype=torch.float32)[mine].contiguous())
         w1 = (torch.randn((E, 2 * H, K), generator=gen, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
         w2 = (torch.randn((E, D, H), generator=gen, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
         wts.append(MoEWeights.pack(w1, w2, cfg["kind"], rank=rank if strong else 0, world=world if strong else 1,
@@ -262,6 +267,9 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
     torch.cuda.synchronize()
 
     def step(i, a=None):
+        if a2a:     # every rank owns T / world tokens; routed rows travel to the experts' ranks and back
+            return moe_forward(acts[i % sets] if a is None else a, logits[i % sets], wts[i % sets], k, out_dtype=torch.bfloat16,
+                               dispatch="all_to_all")
         # expert-parallel ranks exchange bf16 partial results and keep their own token rows (reduce-scatter)
         return moe_forward(acts[i % sets] if a is None else a, logits[i % sets], wts[i % sets], k, out_dtype=torch.bfloat16,
                            reduce="reduce_scatter", exchange_dtype=torch.bfloat16)
@@ -443,6 +451,27 @@ def cpu_arm(name, steps=1, warmup=0, rows_reference=64, rows_port=512, want_port
         else:
             out["port"] = {"value": val, "unit": "TFLOP/s", "seconds": dt, "sample": sample}
     return out
+
+
+def reference_cuda(name):
+    """The reference's own CUDA kernel for the workload (FP8 dense workloads only), timed on this GPU through the
+    driver program `oracle/_ref/ref_time_fp8`, which compiles the reference's cuda/gemm/fp8_gemm.cu unmodified.  Context
+    beside the CPU arm; None where the binary was not built or the workload has no reference kernel."""
+    cfg = WORKLOADS[name]
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_time_fp8")
+    if cfg["kind"] not in ("fp8", "fp8_block128") or cfg.get("moe") or not os.path.exists(exe):
+        return None
+    M, N, K = cfg["M"], cfg["N"], cfg["K"]
+    try:
+        out = subprocess.run([exe, str(M), str(N), str(K), "128", "1"], capture_output=True, text=True, timeout=180)
+        words = out.stdout.split()
+        ms = float(words[1] if cfg["kind"] == "fp8_block128" else words[3])
+    except Exception as exc:
+        return {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    kernel = ("fp8_gemm_groupwise_kernel (cuda/gemm/fp8_gemm.cu:69-99)" if cfg["kind"] == "fp8_block128"
+              else "fp8_gemm_per_tensor_kernel (cuda/gemm/fp8_gemm.cu:29-65)")
+    return {"value": 2.0 * M * N * K / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ms, "kernel": kernel,
+            "sample": f"the reference's kernel, unmodified, one launch at the full {M} x {K} x {N} on this GPU (operands already quantised)"}
 
 
 def run_reference(args):
@@ -694,7 +723,25 @@ def measure_e2e(wl, timer, K_steps):
     e1.record()
     timer.barrier()
     e2e_ms = timer.reduce_max([e0.elapsed_time(e1) / e2e_steps])[0]
-    return e2e_ms, serial_ms, wl["acts"][0].numel() * 2, host_out.numel() * host_out.element_size()
+    # the host link alone: this step's result copied device -> pinned host and its input host -> device, all ranks at once
+    # (the ceiling the end-to-end figure can reach however fast the kernels are)
+    dev_out = torch.empty(host_out.shape, dtype=host_out.dtype, device=device)
+    timer.barrier()
+    e0.record()
+    for _ in range(3):
+        host_out.copy_(dev_out, non_blocking=True)
+    e1.record()
+    timer.barrier()
+    d2h_ms = timer.reduce_max([e0.elapsed_time(e1) / 3])[0]
+    e0.record()
+    for _ in range(3):
+        dev_a.copy_(host_a[0], non_blocking=True)
+    e1.record()
+    timer.barrier()
+    h2d_ms = timer.reduce_max([e0.elapsed_time(e1) / 3])[0]
+    link = {"d2h_gbs_per_rank": host_out.numel() * host_out.element_size() / (d2h_ms * 1e-3) / 1e9,
+            "h2d_gbs_per_rank": wl["acts"][0].numel() * 2 / (h2d_ms * 1e-3) / 1e9, "d2h_ms": d2h_ms, "h2d_ms": h2d_ms}
+    return e2e_ms, serial_ms, wl["acts"][0].numel() * 2, host_out.numel() * host_out.element_size(), link
 
 
 def host_cost_us(wl, n=200):
@@ -759,7 +806,7 @@ def main():
     wl = head.pop("_wl")
     flops_all = head.pop("_flops_all")
     clocks = head.pop("clocks", None)
-    e2e_ms, serial_ms, h2d, d2h = measure_e2e(wl, timer, K_steps)
+    e2e_ms, serial_ms, h2d, d2h, link = measure_e2e(wl, timer, K_steps)
     host_us = host_cost_us(wl) if not wl.get("layer") else None
     del wl
     torch.cuda.empty_cache()
@@ -792,7 +839,7 @@ def main():
         "ms_per_step_min_median_max": head["ms_per_step_min_median_max"], "burst": head["burst"],
         "roofline": head["roofline"],
         "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "single_step_ms": serial_ms,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "single_step_ms": serial_ms, "host_link_alone": link,
                 "how": "HostPipeline: pinned host buffers, copy-in / compute / copy-out on three streams, two staging buffers"},
         "host_us_per_call": host_us,
         "gpu_launches": head["gpu_launches"], "launches_per_step": head["launches_per_step"],
@@ -808,6 +855,9 @@ def main():
         line["sweep"] = sweep
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_arm(args.workload, steps=1, warmup=1)
+        rc = reference_cuda(args.workload)
+        if rc is not None:
+            line["reference_cuda"] = rc
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -23,6 +23,8 @@
 namespace dsl {
 
 // ---- 16-element vector loads ------------------------------------------------------------
+template <typename T> struct dsl_is_half { static constexpr bool value = false; };
+template <> struct dsl_is_half<__half> { static constexpr bool value = true; };
 template <typename T>
 __device__ __forceinline__ void load16(const T* p, float (&v)[16]);
 
@@ -64,6 +66,117 @@ __device__ __forceinline__ void load16<__half>(const __half* p, float (&v)[16]) 
         }
     }
 }
+// The same 16 elements with 256-bit loads (one for 16-bit types, two for fp32): a warp's request then covers whole
+// 128-byte lines instead of every other 16 bytes of them, which halves the requests the L1 has to replay for these
+// streaming kernels.  The address must be 32-byte aligned (`wide` is decided on the host from the base pointer and the
+// row pitch); the data is read once, so it bypasses L1 allocation.
+__device__ __forceinline__ void ldg256(const void* p, uint32_t (&r)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+template <typename T>
+__device__ __forceinline__ void load16w(const T* p, float (&v)[16], bool wide) {
+    if (!wide) { load16<T>(p, v); return; }
+    if (sizeof(T) == 4) {
+        uint32_t a[8], b[8];
+        ldg256(p, a);
+        ldg256(reinterpret_cast<const uint8_t*>(p) + 32, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { v[i] = __uint_as_float(a[i]); v[8 + i] = __uint_as_float(b[i]); }
+    } else {
+        uint32_t w[8];
+        ldg256(p, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (sizeof(T) == 2 && !dsl_is_half<T>::value) {
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+            } else {
+                float2 f = __half22float2(*reinterpret_cast<__half2*>(&w[j]));
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        }
+    }
+}
+// ---- one thread's 16 elements --------------------------------------------------------------
+// Generic form: 16 floats.  bf16 (the activations' usual type) has a form that keeps the raw 8 words: the block
+// maximum comes from packed |x| / max on bf16 pairs (exact: they are comparisons), and the e2m1 conversion widens,
+// scales two values per instruction (mul.rn.f32x2, the same bits as two __fmul_rn) and merges the nibble pairs with
+// byte permutes.  These kernels run at 0.76 instructions per scheduler and cycle (ncu), so instructions are time.
+__device__ __forceinline__ void mul2(float a0, float a1, unsigned long long s2, float& r0, float& r1) {
+    unsigned long long a, r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a0), "f"(a1));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(s2));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r0), "=f"(r1) : "l"(r));
+}
+__device__ __forceinline__ uint32_t pack4(uint32_t b0, uint32_t b1, uint32_t b2, uint32_t b3) {
+    return __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
+}
+template <typename T>
+struct Chunk16 {
+    float v[16];
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    }
+    __device__ __forceinline__ void load(const T* p, bool wide) { load16w<T>(p, v, wide); }
+    __device__ __forceinline__ float amax() const {
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+        return m;
+    }
+    __device__ __forceinline__ uint2 quant_e2m1(float inv) const {
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t b = cvt_e2m1x2(__fmul_rn(v[2 * i], inv), __fmul_rn(v[2 * i + 1], inv));
+            w[i >> 2] |= b << (8 * (i & 3));
+        }
+        return make_uint2(w[0], w[1]);
+    }
+};
+template <>
+struct Chunk16<__nv_bfloat16> {
+    uint32_t w[8];
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = 0u;
+    }
+    __device__ __forceinline__ void load(const __nv_bfloat16* p, bool wide) {
+        if (wide) {
+            ldg256(p, w);
+        } else {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        }
+    }
+    __device__ __forceinline__ float amax() const {
+        uint32_t m = w[0] & 0x7FFF7FFFu;
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            const uint32_t a = w[i] & 0x7FFF7FFFu;
+            const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&m), *reinterpret_cast<const __nv_bfloat162*>(&a));
+            m = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        return fmaxf(__uint_as_float(m << 16), __uint_as_float(m & 0xFFFF0000u));
+    }
+    __device__ __forceinline__ uint2 quant_e2m1(float inv) const {
+        unsigned long long s2;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(s2) : "f"(inv));
+        uint32_t b[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float lo, hi;
+            mul2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u), s2, lo, hi);
+            b[i] = cvt_e2m1x2(lo, hi);
+        }
+        return make_uint2(pack4(b[0], b[1], b[2], b[3]), pack4(b[4], b[5], b[6], b[7]));
+    }
+};
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);
 template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
@@ -93,22 +206,42 @@ __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
 // Two values of q0 must pass through untouched: a zero (the zero residual is +0 and would turn -0
 // into +0) and an infinity (Inf - Inf poisons the residual); both are the fixed points of q -> 2q.
 // A NaN stays a NaN through the corrections.  Six FMA-pipe instructions, one compare and one select
-// per element instead of a reciprocal and range checks.
-__device__ __forceinline__ float div_for_e4m3(float x, float s, float inv) {
-    const float q0 = __fmul_rn(x, inv);
-    const float q1 = __fmaf_rn(__fmaf_rn(-q0, s, x), inv, q0);
-    const float q2 = __fmaf_rn(__fmaf_rn(-q1, s, x), inv, q1);
-    return __fadd_rn(q0, q0) == q0 ? q0 : q2;
+// per element instead of a reciprocal and range checks (half that with the packed instructions below).
+// Written for two elements at a time with the packed fp32 instructions (mul / fma / add .f32x2: each half is the
+// IEEE operation of the scalar form q0 = x*y, q1 = fma(fma(-q0, s, x), y, q0), q2 likewise from q1, and
+// fma(-q, s, x) == fma(q, -s, x) bit for bit), which halves the instruction count of the E4M3 quantisers - they run
+// close to the issue limit.
+__device__ __forceinline__ void div2_for_e4m3(float x0, float x1, unsigned long long neg_s2, unsigned long long inv2, float& r0,
+                                              float& r1) {
+    unsigned long long x, q0, q1, q2, r, d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(x0), "f"(x1));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q0) : "l"(x), "l"(inv2));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(q0), "l"(neg_s2), "l"(x));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q1) : "l"(r), "l"(inv2), "l"(q0));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(q1), "l"(neg_s2), "l"(x));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q2) : "l"(r), "l"(inv2), "l"(q1));
+    asm("add.rn.f32x2 %0, %1, %1;" : "=l"(d) : "l"(q0));
+    float a0, a1, b0, b1, d0, d1;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(q0));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(b0), "=f"(b1) : "l"(q2));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+    r0 = d0 == a0 ? a0 : b0;
+    r1 = d1 == a1 ? a1 : b1;
 }
 __device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
     uint32_t w[4];
     if (s >= 1e-12f && s <= 3.0e38f) {
         const float inv = __frcp_rn(s);
+        const float ns = -s;
+        unsigned long long inv2, neg_s2;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(inv2) : "f"(inv));
+        asm("mov.b64 %0, {%1, %1};" : "=l"(neg_s2) : "f"(ns));
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            uint32_t lo = cvt_e4m3x2(div_for_e4m3(v[4 * i], s, inv), div_for_e4m3(v[4 * i + 1], s, inv));
-            uint32_t hi = cvt_e4m3x2(div_for_e4m3(v[4 * i + 2], s, inv), div_for_e4m3(v[4 * i + 3], s, inv));
-            w[i] = lo | (hi << 16);
+            float a, b, c, d;
+            div2_for_e4m3(v[4 * i], v[4 * i + 1], neg_s2, inv2, a, b);
+            div2_for_e4m3(v[4 * i + 2], v[4 * i + 3], neg_s2, inv2, c, d);
+            w[i] = static_cast<uint32_t>(cvt_e4m3x2(a, b)) | (static_cast<uint32_t>(cvt_e4m3x2(c, d)) << 16);
         }
     } else {   // an infinite scale (an Inf among the inputs: 0 * Inf would poison the residual), or a given
                // scale too small for the residual argument above (also zero, negative, NaN): divide for real
@@ -135,13 +268,23 @@ __device__ __forceinline__ uint2 quant16_e2m1(const float (&v)[16], float inv) {
 // Non-negative floats order like their bit patterns, so the reduction is an integer
 // atomicMax (same trick as cuda/gemm/fp8_gemm.cu:132) and the result is order-independent.
 template <typename T>
-__global__ void __launch_bounds__(256) amax_kernel(const T* __restrict__ x, size_t n, uint32_t* amax_bits) {
+__global__ void __launch_bounds__(256) amax_kernel(const T* __restrict__ x, size_t n, uint32_t* amax_bits, bool wide) {
     float m = 0.f;
     const size_t nvec = n / 16;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
-        float v[16];
-        load16<T>(x + i * 16, v);
-        m = fmaxf(m, amax16(v));
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {    // four chunks (128 bytes of bf16) in flight per thread
+        Chunk16<T> a, b, c, d;
+        a.load(x + i * 16, wide);
+        b.load(x + (i + stride) * 16, wide);
+        c.load(x + (i + 2 * stride) * 16, wide);
+        d.load(x + (i + 3 * stride) * 16, wide);
+        m = fmaxf(fmaxf(m, fmaxf(a.amax(), b.amax())), fmaxf(c.amax(), d.amax()));
+    }
+    for (; i < nvec; i += stride) {
+        Chunk16<T> a;
+        a.load(x + i * 16, wide);
+        m = fmaxf(m, a.amax());
     }
     if (blockIdx.x == 0 && threadIdx.x == 0)
         for (size_t i = nvec * 16; i < n; ++i) m = fmaxf(m, fabsf(to_f32<T>(x[i])));
@@ -200,7 +343,7 @@ quant_fp8_tensor_kernel(const T* __restrict__ x, size_t n, const uint32_t* amax_
 template <typename T>
 __global__ void __launch_bounds__(256)
 quant_fp8_1x128_kernel(const T* __restrict__ x, long long M, int K, uint8_t* __restrict__ q,
-                       float* __restrict__ scales, int log2_cp) {
+                       float* __restrict__ scales, int log2_cp, bool wide) {
     griddep_launch_dependents();   // the GEMM that follows may set itself up now; it waits before reading q / scales
     const int cpr = K / 16;
     const int ng = (K + 127) / 128;
@@ -211,7 +354,7 @@ quant_fp8_1x128_kernel(const T* __restrict__ x, long long M, int K, uint8_t* __r
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = 0.f;
     const size_t off = static_cast<size_t>(row) * K + static_cast<size_t>(kc) * 16;
-    if (valid) load16<T>(x + off, v);
+    if (valid) load16w<T>(x + off, v, wide);
     float m = amax16(v);   // the 8 lanes of a group are adjacent (slots per row are a multiple of 8)
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
@@ -290,7 +433,7 @@ template <typename T, int FMT>   // FMT 0: NVFP4 (block 16, UE4M3 + global scale
 __global__ void __launch_bounds__(256)
 quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict__ gs_ptr,
                  const uint32_t* __restrict__ amax_bits, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
-                 int num_groups, int log2_cp) {
+                 int num_groups, int log2_cp, bool wide) {
     griddep_launch_dependents();   // a GEMM that opted in may set itself up (and stream its weight) from now on
     __shared__ int s_offs[kMaxGroups + 1];
     __shared__ int s_tile0[kMaxGroups + 1];
@@ -340,11 +483,10 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict_
     const long long row = rb * rpb + (threadIdx.x >> log2_cp);
     const bool valid = row < M && kc < cpr;
     const size_t id = static_cast<size_t>(row) * cpr + kc;
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-    if (valid) load16<T>(x + id * 16, v);
-    float m = amax16(v);
+    Chunk16<T> ch;
+    ch.zero();
+    if (valid) ch.load(x + id * 16, wide);
+    float m = ch.amax();
     float inv;
     uint32_t sfb;
     int blk;
@@ -366,7 +508,7 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict_
         blk = kc >> 1;
         writer = (kc & 1) == 0;
     }
-    if (valid) *reinterpret_cast<uint2*>(q + id * 8) = quant16_e2m1(v, inv);
+    if (valid) *reinterpret_cast<uint2*>(q + id * 8) = ch.quant_e2m1(inv);
     // Scale bytes: four consecutive K-blocks of a row are four consecutive bytes of the tile
     // layout, so when the row length allows it one lane stores all four as a word.
     constexpr int LANES_PER_BLK = FMT == 0 ? 1 : 2;
@@ -531,19 +673,21 @@ template <typename T>
 static cudaError_t quant_fp8_typed(const T* x, long long rows, long long cols, int mode, float* scale_io,
                                    int scale_given, uint8_t* q, uint32_t* ws, cudaStream_t st) {
     const size_t n = static_cast<size_t>(rows) * cols;
+    // 256-bit loads need every 16-element chunk on a 32-byte boundary: base pointer and row pitch
+    const bool wide = (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (static_cast<size_t>(cols) * sizeof(T)) % 32 == 0;
     if (mode == DSL_FP8_PER_TENSOR) {
         const int grid = grid_for(n / 16, 256, 148 * 16);
         if (!scale_given) {
             cudaError_t e = cudaMemsetAsync(ws, 0, 4, st);
             if (e != cudaSuccess) return e;
-            amax_kernel<T><<<grid, 256, 0, st>>>(x, n, ws);
+            amax_kernel<T><<<grid, 256, 0, st>>>(x, n, ws, wide);
         }
         quant_fp8_tensor_kernel<T><<<grid, 256, 0, st>>>(x, n, scale_given ? nullptr : ws, scale_io, q);
     } else if (mode == DSL_FP8_GROUP_1X128) {
         const RowMap rm = make_row_map(cols, 3);
         const dim3 grid = row_map_grid(rm, rows, cols);
         if (grid.x > 0 && grid.y > 0)
-            quant_fp8_1x128_kernel<T><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), q, scale_io, rm.log2_cp);
+            quant_fp8_1x128_kernel<T><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), q, scale_io, rm.log2_cp, wide);
     } else {
         dim3 grid(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>((rows + 127) / 128));
         if (grid.x > 0 && grid.y > 0)
@@ -566,6 +710,7 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
                                    int gs_given, uint8_t* q, uint8_t* sf, size_t sf_bytes, int sf_needs_clear,
                                    const int* group_offsets, int num_groups, uint32_t* ws, cudaStream_t st) {
     const size_t n = static_cast<size_t>(rows) * cols;
+    const bool wide = (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (static_cast<size_t>(cols) * sizeof(T)) % 32 == 0;
     cudaError_t e;
     if (format == DSL_FP4_NV && !gs_given && group_offsets == nullptr && n > (32u << 10) && n <= (256u << 10)) {
         const unsigned clear16 = sf_needs_clear ? static_cast<unsigned>(sf_bytes / 16) : 0u;
@@ -583,7 +728,7 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
     if (format == DSL_FP4_NV && !gs_given) {
         e = cudaMemsetAsync(ws, 0, 4, st);
         if (e != cudaSuccess) return e;
-        amax_kernel<T><<<grid_for(n / 16, 256, 148 * 16), 256, 0, st>>>(x, n, ws);
+        amax_kernel<T><<<grid_for(n / 16, 256, 148 * 8), 256, 0, st>>>(x, n, ws, wide);   // one resident wave
     }
     const uint32_t* amax_bits = (format == DSL_FP4_NV && !gs_given) ? ws : nullptr;
     const RowMap rm = make_row_map(cols, 1);
@@ -592,9 +737,9 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
     if (grid.x > cap) grid.x = cap;
     if (grid.x > 0 && grid.y > 0) {
         if (format == DSL_FP4_NV)
-            quant_fp4_kernel<T, 0><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, amax_bits, q, sf, group_offsets, num_groups, rm.log2_cp);
+            quant_fp4_kernel<T, 0><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, amax_bits, q, sf, group_offsets, num_groups, rm.log2_cp, wide);
         else
-            quant_fp4_kernel<T, 1><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, nullptr, q, sf, group_offsets, num_groups, rm.log2_cp);
+            quant_fp4_kernel<T, 1><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, nullptr, q, sf, group_offsets, num_groups, rm.log2_cp, wide);
     }
     return cudaGetLastError();
 }

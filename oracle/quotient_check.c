@@ -1,5 +1,5 @@
 /* Test infrastructure (not part of the product): brute-force check that the division-free quotient used by the
- * E4M3 quantisers (dsl_tool_b200/csrc/quant.cu, div_for_e4m3) equals the IEEE quotient x / s.
+ * E4M3 quantisers (dsl_tool_b200/csrc/quant.cu, div2_for_e4m3) equals the IEEE quotient x / s.
  *
  *   y  = RN(1 / s)                       one reciprocal per 16 elements on the GPU
  *   q0 = RN(x * y)

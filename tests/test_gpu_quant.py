@@ -76,6 +76,26 @@ def test_fp4_formats(cuda_device, shape, dtype, fmt):
     assert (q.cpu().numpy() == qo).all()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_input_that_is_only_16_byte_aligned(cuda_device, dtype):
+    """The quantisers read 32 bytes per thread with one 256-bit load when every chunk sits on a 32-byte boundary and
+    fall back to 16-byte loads otherwise.  A tensor that starts 16 bytes into an allocation takes the fallback: same bytes."""
+    from dsl_tool_b200 import quantize_fp4, quantize_fp8
+    rows, cols = 200, 512
+    xc, _ = _inputs((rows, cols), dtype, 5)
+    shift = 16 // xc.element_size()
+    pool = torch.empty(rows * cols + shift, dtype=dtype, device="cuda")
+    view = pool[shift:].view(rows, cols)
+    view.copy_(xc)
+    assert view.data_ptr() % 32 == 16 and xc.data_ptr() % 32 == 0
+    for fmt in ("nvfp4", "mxfp4"):
+        a, b = quantize_fp4(xc, fmt), quantize_fp4(view, fmt)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and (fmt == "mxfp4" or torch.equal(a[2], b[2]))
+    for mode in ("per_tensor", "groupwise"):
+        a, b = quantize_fp8(xc, mode), quantize_fp8(view, mode)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
 def test_nvfp4_given_global_scale_and_zero_tensor(cuda_device):
     from dsl_tool_b200 import quantize_fp4
     xc, xo = _inputs((64, 128), torch.bfloat16, 4)
