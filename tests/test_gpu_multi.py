@@ -102,3 +102,26 @@ def test_two_gpu_split_matches_single_gpu(cuda_device, tmp_path):
                                       stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=300)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(o[-1500:] for o in outs)
+
+
+def test_one_process_driving_two_devices(cuda_device):
+    """Kernel attributes, occupancy and SM counts are kept per device: a process that has used the library on one GPU
+    gets the same results, bit for bit, on a second one (every kernel family: pair, group-scaled pair, decode, 1-CTA)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from dsl_tool_b200 import _lib, linear, pack_weight
+    g = torch.Generator().manual_seed(3)
+    w = (torch.randn(640, 512, generator=g) * 0.02).bfloat16()
+    outs = {}
+    for dev in ("cuda:0", "cuda:1"):
+        torch.cuda.set_device(dev)
+        for fmt in ("nvfp4", "mxfp4", "fp8", "fp8_block128", "bf16"):
+            pw = pack_weight(w.to(dev), fmt)
+            for M in (5, 100, 300):
+                a = torch.randn(M, 512, generator=torch.Generator().manual_seed(M)).bfloat16().to(dev)
+                outs[(dev, fmt, M)] = linear(a, pw, out_dtype="float32").cpu()
+        _lib.check_status(torch.device(dev))
+    torch.cuda.set_device(0)
+    for (dev, fmt, M), v in outs.items():
+        if dev == "cuda:1":
+            assert torch.equal(v, outs[("cuda:0", fmt, M)]), (fmt, M)
