@@ -42,3 +42,18 @@ def test_reference_arm_other_ranks_are_silent():
 def test_product_arm_refuses_without_a_gpu():
     r = _run(["--steps", "1", "--warmup", "1"], timeout=300)
     assert r.returncode != 0 and "CUDA" in r.stderr and '"value"' not in r.stdout
+
+
+def test_both_arms_describe_the_workload_with_the_same_config_object():
+    """The product arm and the reference arm build `config` with one function; the reference arm's line (above) carries
+    it, and it names the workload's shape and format, so the two lines can be matched by comparing `config`."""
+    sys.path.insert(0, ROOT)
+    import bench
+    for name in ("fp8_groupwise_llama8b_mlp", "nvfp4_8192", "moe_nvfp4", "moe_layer_nvfp4"):
+        for scaling in ("strong", "weak"):
+            c = bench.workload_config(name, scaling, 4)
+            assert c == bench.workload_config(name, scaling, 4)
+            assert c["workload"] == name and c["format"] == bench.WORKLOADS[name]["kind"] and {"M", "K", "N"} <= set(c)
+    r = _run(["--impl", "reference", "--steps", "1", "--warmup", "1"])
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["config"] == bench.workload_config("fp8_groupwise_llama8b_mlp", line["scaling"], 4)
