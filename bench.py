@@ -71,6 +71,7 @@ WORKLOADS = {
     # the MoE GEMM fed the way a layer feeds it: 16384 token rows + their routing; the tokens are quantised ONCE and the
     # packed rows dispatched to expert-sorted order (step = plan + quantise + dispatch + grouped GEMM)
     "moe_nvfp4_tokens": dict(kind="nvfp4", tokens_in=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
+    "moe_fp8_groupwise_tokens": dict(kind="fp8_block128", tokens_in=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
     # the whole MoE feed-forward layer around the two grouped GEMMs (router, plan, quantise once, dispatch,
     # gate/up GEMM with SwiGLU and NVFP4 result, down GEMM, combine); 0.01 = calibrated hidden global scale
     "moe_layer_nvfp4": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
@@ -84,7 +85,7 @@ DEFAULT_WORKLOAD = "fp8_groupwise_llama8b_mlp"
 # further configurations reported in `sweep` (one GPU) ...
 SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_8192_static_scale", "nvfp4_m1", "nvfp4_m16", "nvfp4_m128", "nvfp4_m1024",
               "mxfp4_llama70b_up", "mxfp4_llama70b_down", "moe_nvfp4", "moe_nvfp4_tokens", "moe_nvfp4_skewed",
-              "moe_fp8_groupwise", "moe_layer_nvfp4"]
+              "moe_fp8_groupwise", "moe_fp8_groupwise_tokens", "moe_layer_nvfp4"]
 # ... and the sharded ones when the problem is split over several GPUs
 SWEEP_SHARDED = ["mxfp4_llama70b_up", "mxfp4_llama70b_up_gather", "mxfp4_llama70b_down", "moe_nvfp4", "moe_fp8_groupwise",
                  "moe_layer_nvfp4", "moe_layer_nvfp4_a2a"]
@@ -280,10 +281,13 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
 
 
 def build_token_moe_workload(cfg, rank, device, sets):
-    """Grouped GEMM of an MoE layer from token-level input: x [tokens, K], ids [tokens, k] (seeded top-k routing)."""
-    from dsl_tool_b200 import moe, pack_weight, quantize_fp4
-    from dsl_tool_b200.gemm_kernels import gemm_fp4_quantized
+    """Grouped GEMM of an MoE layer from token-level input: x [tokens, K], ids [tokens, k] (seeded top-k routing).
+    The tokens are quantised ONCE (16384 rows) and the quantised rows - packed e2m1 bytes + scale tiles, or E4M3 bytes +
+    1x128 scale rows - are dispatched to expert-sorted order; the grouped GEMM consumes them as they are."""
+    from dsl_tool_b200 import moe, pack_weight, quantize_fp4, quantize_fp8
+    from dsl_tool_b200.gemm_kernels import gemm_fp4_quantized, gemm_fp8_groupwise_quantized
     T, E, k, K, N = cfg["tokens"], cfg["experts"], cfg["topk"], cfg["K"], cfg["N"]
+    kind = cfg["kind"]
     acts, ids, wts = [], [], []
     for s in range(sets):
         gen = torch.Generator(device=device).manual_seed(55 + s + 1000 * rank)
@@ -291,26 +295,33 @@ def build_token_moe_workload(cfg, rank, device, sets):
         logits = torch.randn((T, E), generator=gen, device=device, dtype=torch.float32)
         ids.append(torch.topk(logits, k, dim=1).indices.to(torch.int32).contiguous())
         w = (torch.randn((E, N, K), generator=gen, device=device, dtype=torch.float32) * cfg["wstd"]).to(torch.bfloat16)
-        wts.append(pack_weight(w, "nvfp4", layout="nk"))
+        wts.append(pack_weight(w, kind, layout="nk"))
         del w
     ones = torch.ones((T, k), dtype=torch.float32, device=device)
     torch.cuda.synchronize()
 
     def quant(i, a=None):
         p = moe.plan(ids[i % sets], ones, E)
-        packed, sf, gs = quantize_fp4(acts[i % sets] if a is None else a, "nvfp4")
-        q, s = moe.dispatch_fp4(p, packed, sf, K, "nvfp4", 0, E)
-        return q, s, gs, p.offsets
+        x = acts[i % sets] if a is None else a
+        if kind == "nvfp4":
+            packed, sf, gs = quantize_fp4(x, "nvfp4")
+            q, s = moe.dispatch_fp4(p, packed, sf, K, "nvfp4", 0, E)
+            return q, s, gs, p.offsets
+        qa, sa = quantize_fp8(x, "groupwise")                  # [T, K] bytes, [T, K/128] fp32 (128-byte rows)
+        return moe.dispatch_rows(p, qa, 0, E), moe.dispatch_rows(p, sa, 0, E), None, p.offsets
 
     def gemm(i, qs):
         w = wts[i % sets]
-        return gemm_fp4_quantized(qs[0], w.q, qs[1], w.scale, format="nvfp4", n=N, global_scale_a=qs[2],
-                                  global_scale_b=w.global_scale, expert_offsets=qs[3], out_dtype=torch.bfloat16, b_static=True)
+        if kind == "nvfp4":
+            return gemm_fp4_quantized(qs[0], w.q, qs[1], w.scale, format="nvfp4", n=N, global_scale_a=qs[2],
+                                      global_scale_b=w.global_scale, expert_offsets=qs[3], out_dtype=torch.bfloat16, b_static=True)
+        return gemm_fp8_groupwise_quantized(qs[0], w.q, qs[1], w.scale, n=N, sb_block=True, expert_offsets=qs[3],
+                                            out_dtype=torch.bfloat16)
 
     def step(i, a=None):
         return gemm(i, quant(i, a))
 
-    return dict(step=step, acts=acts, wts=wts, offs=None, M=T * k, K=K, N=N, kind="nvfp4", flops=2.0 * T * k * N * K, moe=True,
+    return dict(step=step, acts=acts, wts=wts, offs=None, M=T * k, K=K, N=N, kind=kind, flops=2.0 * T * k * N * K, moe=True,
                 act=None, out=None, split=(quant, gemm))
 
 
