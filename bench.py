@@ -51,6 +51,8 @@ WORKLOADS = {
     "nvfp4_8192": dict(kind="nvfp4", M=8192, K=8192, N=8192, wstd=0.02, outliers=True),
     # the same with a calibrated (static) global scale of the activations: the quantiser is one pass over them
     "nvfp4_8192_static_scale": dict(kind="nvfp4", M=8192, K=8192, N=8192, wstd=0.02, outliers=True, act_gs=20.0 / 2688.0),
+    # ... and with one dynamic global scale per token (row): also one pass, no calibration needed
+    "nvfp4_8192_token_scale": dict(kind="nvfp4", M=8192, K=8192, N=8192, wstd=0.02, outliers=True, act_gs="per_token"),
     "nvfp4_m1024": dict(kind="nvfp4", M=1024, K=8192, N=8192, wstd=0.02, outliers=True),
     "nvfp4_m128": dict(kind="nvfp4", M=128, K=8192, N=8192, wstd=0.02, outliers=True),
     "nvfp4_m16": dict(kind="nvfp4", M=16, K=8192, N=8192, wstd=0.02, outliers=True),
@@ -60,6 +62,9 @@ WORKLOADS = {
     # the up projection with the full result wanted on every rank: one NCCL all-gather of the column shards per step
     "mxfp4_llama70b_up_gather": dict(kind="mxfp4", M=8192, K=8192, N=28672, wstd=0.015, outliers=False, gather=True),
     "moe_nvfp4": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
+    # expert-sorted rows quantised with per-token global scales (one pass over the 1.07 GB of routed rows)
+    "moe_nvfp4_token_scale": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02,
+                                  act_gs="per_token"),
     # the same layer under skewed routing: per-expert logit bias N(0, 0.6), one expert nobody is routed to
     "moe_nvfp4_skewed": dict(kind="nvfp4", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02, skew=0.6),
     "moe_fp8_groupwise": dict(kind="fp8_block128", moe=True, tokens=16384, topk=8, experts=64, K=4096, N=3072, wstd=0.02),
@@ -83,8 +88,8 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "fp8_groupwise_llama8b_mlp"
 # further configurations reported in `sweep` (one GPU) ...
-SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_8192_static_scale", "nvfp4_m1", "nvfp4_m16", "nvfp4_m128", "nvfp4_m1024",
-              "mxfp4_llama70b_up", "mxfp4_llama70b_down", "moe_nvfp4", "moe_nvfp4_tokens", "moe_nvfp4_skewed",
+SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_8192_static_scale", "nvfp4_8192_token_scale", "nvfp4_m1", "nvfp4_m16", "nvfp4_m128", "nvfp4_m1024",
+              "mxfp4_llama70b_up", "mxfp4_llama70b_down", "moe_nvfp4", "moe_nvfp4_token_scale", "moe_nvfp4_tokens", "moe_nvfp4_skewed",
               "moe_fp8_groupwise", "moe_fp8_groupwise_tokens", "moe_layer_nvfp4"]
 # ... and the sharded ones when the problem is split over several GPUs
 SWEEP_SHARDED = ["mxfp4_llama70b_up", "mxfp4_llama70b_up_gather", "mxfp4_llama70b_down", "moe_nvfp4", "moe_fp8_groupwise",
@@ -355,6 +360,9 @@ def split_step(wl):
         if kind == "fp8_block128":
             return GK.gemm_fp8_groupwise_quantized(q[0], w.q, q[1], w.scale, sb_block=True, **common)
         if kind in ("nvfp4", "mxfp4"):
+            if wl.get("act_gs") == "per_token":
+                return GK.gemm_fp4_quantized(q[0], w.q, q[1], w.scale, format=kind, token_scale=q[2],
+                                             global_scale_b=w.global_scale, b_static=True, **common)
             return GK.gemm_fp4_quantized(q[0], w.q, q[1], w.scale, format=kind, global_scale_a=q[2],
                                          global_scale_b=w.global_scale, b_static=True, **common)
         return GK.gemm_bf16_raw(q[0], w.q, **common)
@@ -617,6 +625,9 @@ def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, 
     gemm_ms_burst, _ = kernel_pass() if full else (None, None)
     mark0 = sampler.mark() if sampler is not None else 0
     times, mine = timer.blocks(runner, K, min_seconds)
+    eager_ms = None
+    if graph:       # the same steps launched one by one from the host (what a caller without a graph gets)
+        eager_ms = timer.reduce_max([timer.block(run_eager, K)])[0] / K
     gemm_ms, quant_ms = kernel_pass()
     mark1 = sampler.mark() if sampler is not None else 0
     _lib.check_status(device)
@@ -639,6 +650,8 @@ def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, 
         "kernel_ms": gemm_ms_max, "quant_kernel_ms": quant_ms_max, "cuda_graph": bool(graph),
         "host_gap_ms": max(0.0, ms_med - gemm_ms_max - quant_ms_max),
     }
+    if eager_ms is not None:
+        rec["eager_ms_per_step"] = eager_ms
     achieved = wl["flops"] / (gemm_ms * 1e-3) / 1e12
     # The kernel is timed inside a region of a second or more (sustained clocks, usually at the power cap), so the
     # denominator is the cuBLAS bf16 rate measured the same way; the headline workload also carries the pair
@@ -782,6 +795,8 @@ def main():
     ap.add_argument("--sets", type=int, default=4, help="rotating input sets (keeps operands out of L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="only the headline workload")
+    ap.add_argument("--sweep-limit", type=float, default=420.0,
+                    help="seconds after which the line is printed with the sweep entries measured so far")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="the K-step block is repeated until the timed region is this long")
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
                     help="strong (default): the one problem is split across the ranks (columns / experts); "
@@ -822,8 +837,52 @@ def main():
     del wl
     torch.cuda.empty_cache()
 
+    # The headline line is complete here; the sweep only adds to it.  A watchdog guarantees that the line is printed
+    # (and every rank exits) even if a sweep entry fails on one rank and leaves the others waiting in a collective.
+    line = None
+    if rank == 0:
+        line = {
+            "metric": "gemm_tflops", "value": head["value"], "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+            "dtype": DTYPE_NAME[head["format"]], "data": "synthetic",
+            "config": workload_config(args.workload, args.scaling, args.sets),
+            "repeats": head["repeats"], "timed_region_s": head["timed_region_s"],
+            "ms_per_step_min_median_max": head["ms_per_step_min_median_max"], "burst": head["burst"],
+            "roofline": head["roofline"],
+            "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "single_step_ms": serial_ms, "host_link_alone": link,
+                    "how": "HostPipeline: pinned host buffers, copy-in / compute / copy-out on three streams, two staging buffers"},
+            "host_us_per_call": host_us,
+            "gpu_launches": head["gpu_launches"], "launches_per_step": head["launches_per_step"],
+            "cuda_graph": bool(args.graph),
+            "clocks": clocks if clocks is not None else (sampler.summary() if sampler is not None else None),
+        }
+        if "roofline_tensor" in head:
+            line["roofline_tensor"] = head["roofline_tensor"]
+        if "per_rank" in head:
+            line["per_rank"] = head["per_rank"]
+            line["kernel_ms"], line["quant_kernel_ms"], line["host_gap_ms"] = head["kernel_ms"], head["quant_kernel_ms"], head["host_gap_ms"]
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_arm(args.workload, steps=1, warmup=1)
+            rc = reference_cuda(args.workload)
+            if rc is not None:
+                line["reference_cuda"] = rc
+
     sweep = []
+    printed = threading.Lock()
+
+    def give_up():
+        if printed.acquire(blocking=False):
+            if line is not None:
+                line["sweep"] = sweep
+                line["sweep_error"] = f"the sweep did not finish within {args.sweep_limit:.0f} s; entries measured so far are kept"
+                print(json.dumps(line), flush=True)
+            os._exit(0)
+
     if not args.no_sweep and args.workload == DEFAULT_WORKLOAD:
+        watchdog = threading.Timer(args.sweep_limit, give_up)
+        watchdog.daemon = True
+        watchdog.start()
         names = SWEEP_1GPU if world == 1 else SWEEP_SHARDED
         for name in names:
             c = WORKLOADS[name]
@@ -835,41 +894,15 @@ def main():
             except Exception as exc:     # a sweep entry must not take the headline down with it
                 rec = {"workload": name, "error": f"{type(exc).__name__}: {exc}"}
             sweep.append(rec)
-    clocks_all = sampler.stop() if sampler is not None else None
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
-
-    line = {
-        "metric": "gemm_tflops", "value": head["value"], "unit": "TFLOP/s", "n_gpus": world, "steps": K_steps, "warmup": W,
-        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-        "dtype": DTYPE_NAME[head["format"]], "data": "synthetic",
-        "config": workload_config(args.workload, args.scaling, args.sets),
-        "repeats": head["repeats"], "timed_region_s": head["timed_region_s"],
-        "ms_per_step_min_median_max": head["ms_per_step_min_median_max"], "burst": head["burst"],
-        "roofline": head["roofline"],
-        "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "single_step_ms": serial_ms, "host_link_alone": link,
-                "how": "HostPipeline: pinned host buffers, copy-in / compute / copy-out on three streams, two staging buffers"},
-        "host_us_per_call": host_us,
-        "gpu_launches": head["gpu_launches"], "launches_per_step": head["launches_per_step"],
-        "cuda_graph": bool(args.graph),
-        "clocks": clocks if clocks is not None else clocks_all,
-    }
-    if "roofline_tensor" in head:
-        line["roofline_tensor"] = head["roofline_tensor"]
-    if "per_rank" in head:
-        line["per_rank"] = head["per_rank"]
-        line["kernel_ms"], line["quant_kernel_ms"], line["host_gap_ms"] = head["kernel_ms"], head["quant_kernel_ms"], head["host_gap_ms"]
-    if sweep:
-        line["sweep"] = sweep
-    if not args.no_cpu_baseline and world == 1:
-        line["cpu_baseline"] = cpu_arm(args.workload, steps=1, warmup=1)
-        rc = reference_cuda(args.workload)
-        if rc is not None:
-            line["reference_cuda"] = rc
-    print(json.dumps(line))
+        watchdog.cancel()
+    if not printed.acquire(blocking=False):
+        return                                    # the watchdog is printing / has printed
+    if sampler is not None:
+        sampler.stop()
+    if rank == 0:
+        if sweep:
+            line["sweep"] = sweep
+        print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 

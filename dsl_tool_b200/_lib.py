@@ -25,6 +25,7 @@ OUT_NVFP4 = 3
 MAX_GROUPS = 1024
 STATIC_SCRATCH_BYTES = 4 << 20
 WS_HEADER_BYTES = 64 << 10
+PER_TOKEN_MAX_COLS = 32768
 
 _ERR_NAMES = {
     -1: "a required pointer is NULL",
@@ -54,6 +55,7 @@ class Epilogue(ctypes.Structure):
         ("out_sf", ctypes.c_void_p),
         ("out_gs_host", ctypes.c_float),
         ("out_gs_dev", ctypes.c_void_p),
+        ("act_scale_per_token", ctypes.c_int),
     ]
 
 
@@ -82,6 +84,7 @@ _SIGNATURES = {
     "dsl_sf_bytes_grouped": (ctypes.c_size_t, [_ll, _ll, _i]),
     "dsl_quant_fp8": (_i, [_vp, _i, _ll, _ll, _i, _vp, _i, _vp, _vp, _vp]),
     "dsl_quant_fp4": (_i, [_vp, _i, _ll, _ll, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp]),
+    "dsl_quant_fp4_per_token": (_i, [_vp, _i, _ll, _ll, _vp, _vp, _vp, _vp, _i, _vp]),
     "dsl_transpose_u8": (_i, [_vp, _vp, _i, _i, _vp]),
     "dsl_gemm_fp8": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),
     "dsl_gemm_fp8_groupwise": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _ll, _ll, _i, _i, _vp, _i,

@@ -65,6 +65,29 @@ int dsl_quant_fp4(const void* x, int dtype, long long rows, long long cols, int 
                                              as_stream(stream)));
 }
 
+int dsl_quant_fp4_per_token(const void* x, int dtype, long long rows, long long cols, float* gs_out, uint8_t* q_out,
+                            uint8_t* sf_out, const int* group_offsets, int groups, void* stream) {
+    if (x == nullptr || q_out == nullptr || sf_out == nullptr || gs_out == nullptr) return DSL_ERR_NULL;
+    if (dtype < DSL_F32 || dtype > DSL_F16) return DSL_ERR_ENUM;
+    if (rows < 0 || cols < 0 || rows > (1ll << 31) || cols % 32 != 0) return DSL_ERR_SHAPE;
+    if (cols > DSL_PER_TOKEN_MAX_COLS) return DSL_ERR_TOO_LARGE;      // a row is held in one CTA's registers
+    if (group_offsets != nullptr && (groups < 1 || groups > DSL_MAX_GROUPS)) return DSL_ERR_TOO_LARGE;
+    if (!aligned16(x) || !aligned16(q_out) || !aligned16(sf_out)) return DSL_ERR_ALIGN;
+    if (rows == 0 || cols == 0) return 0;
+    const long long nblk = cols / 16;
+    size_t sf_bytes;
+    int clear;
+    if (group_offsets != nullptr) {
+        sf_bytes = dsl_sf_bytes_grouped(rows, nblk, groups);
+        clear = 1;
+    } else {
+        sf_bytes = dsl_sf_bytes(rows, nblk);
+        clear = (rows % 128 != 0 || nblk % 4 != 0) ? 1 : 0;
+    }
+    return static_cast<int>(launch_quant_nvfp4_per_token(x, dtype, rows, cols, gs_out, q_out, sf_out, sf_bytes, clear, group_offsets,
+                                                         groups, as_stream(stream)));
+}
+
 int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream) {
     if (in == nullptr || out == nullptr) return DSL_ERR_NULL;
     if (R < 0 || C < 0) return DSL_ERR_SHAPE;

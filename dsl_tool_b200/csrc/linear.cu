@@ -16,10 +16,11 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Carve {
     size_t q_bytes, scale_bytes, total;
-    size_t off_scale, off_gs, off_ws;
+    size_t off_scale, off_gs, off_ws, off_rows;
 };
 
-// Layout of the activation scratch: quantised bytes | scales | global / tensor scale (4 B) | amax cell (16 B)
+// Layout of the activation scratch: quantised bytes | scales | global / tensor scale (4 B) | amax cell (16 B) |
+// per-token global scales (NVFP4 only)
 bool carve(int format, long long M, int K, int groups, Carve* c) {
     if (M < 0 || K <= 0) return false;
     const size_t m = static_cast<size_t>(M);
@@ -40,7 +41,8 @@ bool carve(int format, long long M, int K, int groups, Carve* c) {
     c->off_scale = align_up(c->q_bytes, 256);
     c->off_gs = c->off_scale + align_up(c->scale_bytes, 256);
     c->off_ws = c->off_gs + 256;
-    c->total = c->off_ws + 256;
+    c->off_rows = c->off_ws + 256;                       // per-token global scales (NVFP4, act_scale_per_token)
+    c->total = c->off_rows + (format == DSL_W_NVFP4 ? align_up(m * sizeof(float), 256) : 0);
     return true;
 }
 }  // namespace
@@ -98,6 +100,20 @@ extern "C" int dsl_linear(const void* x, int x_dtype, long long M, const dsl_wei
             if (fmt == DSL_FP4_NV && w->global_scale == nullptr) return DSL_ERR_NULL;
             // NVFP4: a global scale handed in through ep->scale_a_dev (calibrated, or known from the producer of x)
             // is used as it is, which makes the quantiser ONE pass over x; otherwise it comes from an amax pass
+            if (ep->act_scale_per_token) {
+                if (fmt != DSL_FP4_NV) return DSL_ERR_ENUM;
+                if (ep->row_scale != nullptr) return DSL_ERR_ENUM;      // the per-token factor occupies that slot
+                float* gs_rows = reinterpret_cast<float*>(base + c.off_rows);
+                rc = dsl_quant_fp4_per_token(x, x_dtype, M, w->k, gs_rows, qa, static_cast<uint8_t*>(scales), offs, w->groups, stream);
+                if (rc != 0) return rc;
+                e.scale_a_dev = nullptr;
+                e.scale_a_host = 1.0f;
+                e.scale_b_dev = w->global_scale;
+                e.row_scale = gs_rows;
+                return dsl_gemm_fp4(qa, static_cast<const uint8_t*>(w->q), static_cast<const uint8_t*>(scales),
+                                    static_cast<const uint8_t*>(w->scale), fmt, C, ldc, M, w->n, w->k, offs, w->groups, &e, status,
+                                    stream);
+            }
             const bool gs_given = fmt == DSL_FP4_NV && ep->scale_a_dev != nullptr;
             float* gs_io = gs_given ? const_cast<float*>(ep->scale_a_dev) : gs;
             rc = dsl_quant_fp4(x, x_dtype, M, w->k, fmt, gs_io, gs_given ? 1 : 0, qa, static_cast<uint8_t*>(scales), offs, w->groups,

@@ -527,6 +527,101 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict_
 }
 
 
+// NVFP4 with one global scale PER ROW (per token): gs[m] = amax_row[m] / 2688.  A row's quantisation then depends on
+// that row only, so amax, global scale, block scales, nibbles and scale tiles come out of ONE pass: a CTA takes ROWS rows
+// at a time (grid-stride), every thread keeps its chunks of those rows in registers while the row maxima are reduced
+// through shared memory, then quantises them.  R = chunks per thread and row (row length up to R * 4096 elements).
+template <typename T, int R, int ROWS>
+__global__ void __launch_bounds__(256)
+quant_nvfp4_token_kernel(const T* __restrict__ x, long long M, int K, float* __restrict__ gs_out, uint8_t* __restrict__ q,
+                         uint8_t* __restrict__ sf, const int* __restrict__ group_offsets, int num_groups, bool wide) {
+    griddep_launch_dependents();
+    __shared__ int s_offs[kMaxGroups + 1];
+    __shared__ int s_tile0[kMaxGroups + 1];
+    __shared__ float red[2][ROWS][8];
+    SfIndexer sfi;
+    const int cpr = K / 16;
+    sfi.katoms = (cpr + 3) / 4;
+    sfi.groups = num_groups;
+    sfi.offs = nullptr;
+    sfi.tile0 = nullptr;
+    if (group_offsets != nullptr) {
+        load_group_offsets(s_offs, group_offsets, num_groups, static_cast<int>(M));
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int g = 0; g < num_groups; ++g) {
+                s_tile0[g] = t;
+                t += (monotone_rows(s_offs, g) + 127) >> 7;
+            }
+            s_tile0[num_groups] = t;
+        }
+        __syncthreads();
+        sfi.offs = s_offs;
+        sfi.tile0 = s_tile0;
+    }
+    const bool packed = (cpr % 4) == 0;     // four consecutive K-blocks of a row are one word of the tile layout
+    const long long row_groups = (M + ROWS - 1) / ROWS;
+    int it = 0;
+    for (long long rg = blockIdx.x; rg < row_groups; rg += gridDim.x, ++it) {
+        const long long row0 = rg * ROWS;
+        Chunk16<T> ch[ROWS][R];
+        float bm[ROWS][R];
+        float m[ROWS];
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            m[j] = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int kc = threadIdx.x + r * 256;
+                ch[j][r].zero();
+                if (row0 + j < M && kc < cpr) ch[j][r].load(x + (static_cast<size_t>(row0 + j) * cpr + kc) * 16, wide);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                bm[j][r] = ch[j][r].amax();
+                m[j] = fmaxf(m[j], bm[j][r]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m[j] = fmaxf(m[j], __shfl_xor_sync(0xFFFFFFFFu, m[j], o));
+            if (lane_id() == 0) red[it & 1][j][threadIdx.x >> 5] = m[j];
+        }
+        __syncthreads();     // the other buffer is written next time: nobody can still be reading it then
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            const long long row = row0 + j;
+            float a = red[it & 1][j][0];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) a = fmaxf(a, red[it & 1][j][w]);
+            const float gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
+            if (threadIdx.x == 0 && row < M) gs_out[row] = gs;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int kc = threadIdx.x + r * 256;
+                const bool valid = row < M && kc < cpr;
+                float t = __fdiv_rn(__fdiv_rn(bm[j][r], 6.0f), gs);
+                t = fminf(t, 448.0f);
+                const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
+                const float d = __fmul_rn(e4m3_to_float(sfb), gs);
+                const float inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+                if (valid) *reinterpret_cast<uint2*>(q + (static_cast<size_t>(row) * cpr + kc) * 8) = ch[j][r].quant_e2m1(inv);
+                if (packed) {
+                    uint32_t word = sfb;
+                    word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 1) << 8;
+                    word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 2) << 16;
+                    word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 3) << 24;
+                    if (valid && (kc & 3) == 0) *reinterpret_cast<uint32_t*>(sf + sfi(row, kc)) = word;
+                } else if (valid) {
+                    sf[sfi(row, kc)] = static_cast<uint8_t>(sfb);
+                }
+            }
+        }
+    }
+}
+
 // Small tensors (decode: a handful of activation rows): tensor amax, global scale and the NVFP4
 // quantisation in ONE launch of a single CTA, instead of memset + amax + scale + quantise.
 template <typename T>
@@ -751,6 +846,38 @@ cudaError_t launch_quant_fp4(const void* x, int dtype, long long rows, long long
         case DSL_F32: return quant_fp4_typed(static_cast<const float*>(x), rows, cols, format, gs_io, gs_given, q, sf, sf_bytes, sf_needs_clear, group_offsets, num_groups, ws, st);
         case DSL_BF16: return quant_fp4_typed(static_cast<const __nv_bfloat16*>(x), rows, cols, format, gs_io, gs_given, q, sf, sf_bytes, sf_needs_clear, group_offsets, num_groups, ws, st);
         default: return quant_fp4_typed(static_cast<const __half*>(x), rows, cols, format, gs_io, gs_given, q, sf, sf_bytes, sf_needs_clear, group_offsets, num_groups, ws, st);
+    }
+}
+
+template <typename T>
+static cudaError_t quant_token_typed(const T* x, long long rows, long long cols, float* gs_out, uint8_t* q, uint8_t* sf,
+                                     const int* group_offsets, int num_groups, cudaStream_t st) {
+    const bool wide = (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (static_cast<size_t>(cols) * sizeof(T)) % 32 == 0;
+    const long long cpr = cols / 16;
+    const int k = static_cast<int>(cols);
+    // One row per CTA and pass (ROWS = 1).  Taking several rows at a time to keep more loads in flight was measured
+    // and lost (8192 x 8192: 59 -> 68 us, 131072 x 4096: 563 -> 627 us): the kernel is bound by instruction issue, and
+    // the extra registers (128 instead of about 48 per thread) halve the warps that can hide each other's latencies.
+    const unsigned grid = static_cast<unsigned>(rows < 148 * 8 ? rows : 148 * 8);
+    if (cpr <= 256) quant_nvfp4_token_kernel<T, 1, 1><<<grid, 256, 0, st>>>(x, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+    else if (cpr <= 512) quant_nvfp4_token_kernel<T, 2, 1><<<grid, 256, 0, st>>>(x, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+    else if (cpr <= 1024) quant_nvfp4_token_kernel<T, 4, 1><<<grid, 256, 0, st>>>(x, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+    else quant_nvfp4_token_kernel<T, 8, 1><<<grid, 256, 0, st>>>(x, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+    return cudaGetLastError();
+}
+
+// NVFP4 with per-token global scales; cols <= 32768 (checked by the caller).
+cudaError_t launch_quant_nvfp4_per_token(const void* x, int dtype, long long rows, long long cols, float* gs_out, uint8_t* q,
+                                         uint8_t* sf, size_t sf_bytes, int sf_needs_clear, const int* group_offsets,
+                                         int num_groups, cudaStream_t st) {
+    if (sf_needs_clear && sf_bytes > 0) {
+        cudaError_t e = cudaMemsetAsync(sf, 0, sf_bytes, st);
+        if (e != cudaSuccess) return e;
+    }
+    switch (dtype) {
+        case DSL_F32: return quant_token_typed(static_cast<const float*>(x), rows, cols, gs_out, q, sf, group_offsets, num_groups, st);
+        case DSL_BF16: return quant_token_typed(static_cast<const __nv_bfloat16*>(x), rows, cols, gs_out, q, sf, group_offsets, num_groups, st);
+        default: return quant_token_typed(static_cast<const __half*>(x), rows, cols, gs_out, q, sf, group_offsets, num_groups, st);
     }
 }
 

@@ -210,10 +210,12 @@ def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor,
                        format: str, n: int, global_scale_a: Scalar = None, global_scale_b: Scalar = None,
                        out_dtype=torch.float32, expert_offsets: Optional[torch.Tensor] = None,
                        row_scale=None, col_scale=None, b_static: bool = False, activation: Optional[str] = None,
-                       out_global_scale: Scalar = None):
+                       out_global_scale: Scalar = None, token_scale: Optional[torch.Tensor] = None):
     """Block-scaled FP4 GEMM on packed e2m1 operands pa [M, K/2], pb_nk [G*N, K/2] with tiled
     scale bytes; for NVFP4 the result is multiplied once by global_scale_a * global_scale_b.
-    `b_static` as in gemm_fp8_quantized."""
+    `b_static` as in gemm_fp8_quantized.  `token_scale` [M] fp32: the per-token global scales of activations quantised
+    with global_scale="per_token" (then leave global_scale_a unset); they take the epilogue's per-token slot, so
+    `row_scale` cannot be given as well."""
     dev = _lib.require_cuda(pa, pb_nk, sfa, sfb)
     pa, pb_nk = _bytes2d(pa), _bytes2d(pb_nk)
     M, kb2 = pa.shape
@@ -231,6 +233,12 @@ def gemm_fp4_quantized(pa: torch.Tensor, pb_nk: torch.Tensor, sfa: torch.Tensor,
         raise ValueError("scale buffers are smaller than the tiled layout needs")
     nc = _out_cols(n, activation)
     keep: list = []
+    if token_scale is not None:
+        if row_scale is not None or global_scale_a is not None:
+            raise ValueError("token_scale replaces global_scale_a and occupies the row_scale slot")
+        if token_scale.numel() != M:
+            raise ValueError(f"token_scale must have {M} elements, got {token_scale.numel()}")
+        row_scale = token_scale
     ep = _epilogue(dev, global_scale_a, global_scale_b, None, row_scale, col_scale, keep, b_static, activation,
                    (_lib.OP_GEMM_FP4_NV if fmt == _lib.FP4_NV else _lib.OP_GEMM_FP4_MX, M, n, K, groups))
     out, ldc, ret = _make_output(dev, M, nc, out_dtype, out_global_scale, offs, groups, ep, keep)
@@ -288,6 +296,15 @@ def _weight_desc(w: PackedWeight) -> "_lib.Weight":
 
 def _linear_one_call(a: torch.Tensor, w: PackedWeight, out_dtype, offs: Optional[torch.Tensor], row_scale, col_scale,
                      activation: Optional[str], out_global_scale: Scalar, act_global_scale: Scalar = None):
+    per_token = isinstance(act_global_scale, str)
+    if per_token:
+        if act_global_scale != "per_token" or w.format != "nvfp4":
+            raise ValueError("act_global_scale must be a number, a tensor, or 'per_token' (NVFP4 weights)")
+        if row_scale is not None:
+            raise ValueError("per-token activation scales occupy the row_scale slot")
+        if w.k > _lib.PER_TOKEN_MAX_COLS:
+            raise ValueError(f"per-token scales need K <= {_lib.PER_TOKEN_MAX_COLS}")
+        act_global_scale = None
     """Quantise + GEMM through the single C entry point `dsl_linear`: one call into the library, the quantised
     activations in a per-stream arena instead of fresh allocations."""
     dev = a.device
@@ -300,6 +317,7 @@ def _linear_one_call(a: torch.Tensor, w: PackedWeight, out_dtype, offs: Optional
     ep = _lib.Epilogue()
     ep.scale_a_host = ep.scale_b_host = 1.0
     ep.activation = _activation_code(activation)
+    ep.act_scale_per_token = 1 if per_token else 0
     if row_scale is not None:
         row_scale = row_scale.detach().to(device=dev, dtype=torch.float32).contiguous()
         ep.row_scale = row_scale.data_ptr()
@@ -355,7 +373,8 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
     out_dtype "nvfp4" (with `out_global_scale`): the result is quantised in the same epilogue and returned as
     (packed bytes, scale tiles, global scale), the A operand of a following `gemm_fp4_quantized`.
     `act_global_scale` (NVFP4 weights): the fp32 global scale of the activations, a float or a device scalar - a
-    calibrated value instead of amax(a) / 2688.  The quantiser then reads `a` once instead of twice (no amax pass)."""
+    calibrated value instead of amax(a) / 2688 - or "per_token": one dynamic global scale per row (amax_row / 2688).
+    Either way the quantiser reads `a` once instead of twice (no tensor-wide amax pass)."""
     if _activation_code(activation) != _lib.ACT_NONE and not w.gate_up_interleaved:
         raise ValueError("a gated activation needs a weight packed with gate_up_interleave=True")
     if a.dim() != 2 or a.shape[1] != w.k:
@@ -389,6 +408,9 @@ def linear(a: torch.Tensor, w: PackedWeight, *, out_dtype=torch.float32,
     if w.format in ("nvfp4", "mxfp4"):
         pa, sfa, gsa = quantize_fp4(a, w.format, global_scale=act_global_scale if w.format == "nvfp4" else None,
                                     group_offsets=expert_offsets)
+        if isinstance(act_global_scale, str):
+            return gemm_fp4_quantized(pa, w.q, sfa, w.scale, format=w.format, token_scale=gsa, global_scale_b=w.global_scale,
+                                      col_scale=col_scale, b_static=True, **common)
         return gemm_fp4_quantized(pa, w.q, sfa, w.scale, format=w.format, global_scale_a=gsa,
                                   global_scale_b=w.global_scale, row_scale=row_scale, col_scale=col_scale, b_static=True,
                                   **common)

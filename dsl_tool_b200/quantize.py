@@ -75,6 +75,9 @@ def quantize_fp4(x: torch.Tensor, format: str = "nvfp4",
     "nvfp4": unsigned-E4M3 scale per 16 + fp32 global scale (amax/2688 unless given);
     "mxfp4": E8M0 scale per 32.  With `group_offsets` (int32 [G+1], CUDA) rows form ragged
     groups and each group's scales start a fresh 128-row tile.
+    global_scale="per_token" (NVFP4): one global scale per row, amax_row / 2688, returned as an fp32 tensor [rows];
+    the quantiser is then a single pass over x (a tensor-wide dynamic scale needs an amax pass first).  Feed it to
+    the GEMM as `token_scale`.
     """
     if format not in FP4_FORMATS:
         raise ValueError(f"format must be one of {sorted(FP4_FORMATS)}, got {format!r}")
@@ -92,6 +95,18 @@ def quantize_fp4(x: torch.Tensor, format: str = "nvfp4",
     q = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
     sf = torch.empty(sf_bytes(rows, nblk, groups if group_offsets is not None else None),
                      dtype=torch.uint8, device=dev)
+    if isinstance(global_scale, str):
+        if global_scale != "per_token" or format != "nvfp4":
+            raise ValueError("global_scale must be None, a number, a tensor, or 'per_token' (NVFP4 only)")
+        if cols > _lib.PER_TOKEN_MAX_COLS:
+            raise ValueError(f"per-token scales need rows of at most {_lib.PER_TOKEN_MAX_COLS} elements, got {cols}")
+        gs = torch.empty(rows, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().dsl_quant_fp4_per_token(x.data_ptr(), _lib.dtype_code(x.dtype), rows, cols, gs.data_ptr(),
+                                                    q.data_ptr(), sf.data_ptr(), _lib.ptr(group_offsets), groups,
+                                                    _lib.stream_ptr())
+        _lib.check(rc, "dsl_quant_fp4_per_token")
+        return q, sf, gs
     gs = None
     given = 0
     if format == "nvfp4":

@@ -200,11 +200,12 @@ def return_rows(results: torch.Tensor, ex: RowExchange, group=None) -> torch.Ten
 
 def arrival_expert_ids(ex: RowExchange, device) -> torch.Tensor:
     """Local expert index of every received record (int32 [received rows]): records arrive source by source,
-    expert-sorted inside a source."""
+    expert-sorted inside a source.  Built on `device` (the counts travel there once; the output size is already known
+    on the host, so nothing is read back)."""
     world, local = ex.counts_in.shape
-    experts = torch.arange(local, dtype=torch.int32).repeat(world)
-    ids = torch.repeat_interleave(experts, ex.counts_in.reshape(-1).to(torch.int64))
-    return ids.to(device)
+    experts = torch.arange(local, dtype=torch.int32, device=device).repeat(world)
+    counts = ex.counts_in.reshape(-1).to(device=device, dtype=torch.int64, non_blocking=True)
+    return torch.repeat_interleave(experts, counts, output_size=int(sum(ex.recv_rows)))
 
 
 def shard_weight_columns(w_nk: torch.Tensor, rank: int, world: int) -> torch.Tensor:

@@ -79,6 +79,18 @@ int dsl_quant_fp4(const void* x, int dtype, long long rows, long long cols, int 
                   int gs_given, uint8_t* q_out, uint8_t* sf_out, const int* group_offsets, int groups,
                   void* ws, void* stream);
 
+/*
+ * NVFP4 with one global scale per row ("per token"): gs_out[m] = amax of row m / 2688 (1 for an all-zero row), block
+ * scales and values as in dsl_quant_fp4 with that row's global scale.  Same outputs and layouts as dsl_quant_fp4 plus
+ * gs_out [rows] fp32.  Because a row needs nothing but itself, this is ONE pass over x (dsl_quant_fp4 with a dynamic
+ * tensor-wide scale is an amax pass plus a quantise pass); the GEMM applies gs_out as dsl_epilogue.row_scale with
+ * scale_a = 1.  cols <= DSL_PER_TOKEN_MAX_COLS (a row is held in one CTA's registers).  Extends quantize_fp32_to_nvfp4
+ * (cuda/gemm/fp4_gemm.cu:50-90), whose scale is likewise local (per 32 elements).
+ */
+#define DSL_PER_TOKEN_MAX_COLS 32768
+int dsl_quant_fp4_per_token(const void* x, int dtype, long long rows, long long cols, float* gs_out, uint8_t* q_out,
+                            uint8_t* sf_out, const int* group_offsets, int groups, void* stream);
+
 /* Byte-matrix transpose [R, C] -> [C, R]: turns the reference's [K, N] weight layout
  * (cuda/gemm/fp8_gemm.cu:29-35, B[k*N+n]) into the K-major [N, K] the tensor cores read. */
 int dsl_transpose_u8(const uint8_t* in, uint8_t* out, int R, int C, void* stream);
@@ -126,6 +138,9 @@ typedef struct {
                                    Served by dsl_gemm_fp4, dsl_gemm_fp8 and dsl_gemm_bf16 (not the group-scaled FP8 GEMM). */
     float out_gs_host;          /* global scale of the quantised result ... */
     const float* out_gs_dev;    /* ... overridden by this device scalar when non-NULL */
+    int act_scale_per_token;    /* dsl_linear with an NVFP4 weight only: quantise the activations with per-token global
+                                   scales (dsl_quant_fp4_per_token, one pass) and apply them as the per-token rescale;
+                                   row_scale must then be NULL */
 } dsl_epilogue;
 
 /*

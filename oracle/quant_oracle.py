@@ -220,6 +220,14 @@ def nvfp4_global_scale(x) -> np.float32:
     return F32(F32(amax) / F32(448.0 * 6.0))
 
 
+def nvfp4_token_scales(x) -> np.ndarray:
+    """Per-token global scales: amax of each row / 2688 (1 for an all-zero row), fp32 [M]."""
+    x = _f32(x)
+    amax = np.max(np.abs(x), axis=1).astype(F32) if x.shape[1] else np.zeros(x.shape[0], F32)
+    gs = (amax / F32(448.0 * 6.0)).astype(F32)
+    return np.where(amax == 0, F32(1.0), gs).astype(F32)
+
+
 def quant_nvfp4(x, global_scale=None):
     """NVFP4: e2m1 values, one unsigned-E4M3 scale per 16 K-elements, fp32 global scale.
 
@@ -227,16 +235,27 @@ def quant_nvfp4(x, global_scale=None):
     sf  = ue4m3_rne(min((amax_16 / 6) / gs, 448))
     d   = f32(sf) * gs ;  inv = 1/d if d >= FLT_MIN else 0
     q   = e2m1_rne(x * inv)      (saturating at +-6)
-    Returns (packed [M, K/2], sf bytes linear [M, K/16], gs)."""
+    Returns (packed [M, K/2], sf bytes linear [M, K/16], gs).
+
+    global_scale="per_token": the same rule with one global scale PER ROW, gs[m] = amax_row[m] / 2688 (1 for an
+    all-zero row); gs is then an fp32 array [M].  A row's quantisation needs nothing but that row, so the quantiser
+    is one pass over x; the product applies gs[m] as a per-token factor (see gemm_nvfp4)."""
     x = _f32(x)
     M, K = x.shape
     assert K % 16 == 0
-    gs = nvfp4_global_scale(x) if global_scale is None else F32(global_scale)
+    if isinstance(global_scale, str):
+        if global_scale != "per_token":
+            raise ValueError("global_scale must be None, a number or 'per_token'")
+        gs = nvfp4_token_scales(x)
+        gs_b = gs[:, None]
+    else:
+        gs = nvfp4_global_scale(x) if global_scale is None else F32(global_scale)
+        gs_b = gs
     xb = x.reshape(M, K // 16, 16)
     amax = np.max(np.abs(xb), axis=2)
-    t = ((amax / FP4_MAX).astype(F32) / gs).astype(F32)
+    t = ((amax / FP4_MAX).astype(F32) / gs_b).astype(F32)
     sf = e4m3_encode(np.minimum(t, FP8_MAX))
-    d = (e4m3_decode(sf) * gs).astype(F32)
+    d = (e4m3_decode(sf) * gs_b).astype(F32)
     ok = d >= FLT_MIN
     inv = np.where(ok, F32(1.0) / np.where(ok, d, F32(1.0)), F32(0.0)).astype(F32)
     v = (xb * inv[:, :, None]).astype(F32)
@@ -338,9 +357,13 @@ def expand_block_scale(sb_blocks: np.ndarray, N: int, block: int = 128) -> np.nd
 
 
 def gemm_nvfp4(pa, sfa, gsa, pb, sfb, gsb) -> np.ndarray:
-    """Exact operands lut[q]*sf, fp32-accumulated product, times (gsa*gsb) once."""
+    """Exact operands lut[q]*sf, fp32-accumulated product, times (gsa*gsb) once.  With per-token scales (gsa an array
+    [M]) the product is multiplied by gsb and then, row by row, by gsa[m] - the order of the kernels' epilogue
+    (global scales first, per-token factor second)."""
     A = dequant_fp4_values(pa, e4m3_decode(sfa), 16)
     B = dequant_fp4_values(pb, e4m3_decode(sfb), 16)
+    if np.ndim(gsa) == 1:
+        return (((A @ B.T) * F32(gsb)).astype(F32) * _f32(gsa)[:, None]).astype(F32)
     return ((A @ B.T) * F32(F32(gsa) * F32(gsb))).astype(F32)
 
 

@@ -42,6 +42,7 @@ def main():
         q, s = O.quant_fp8_groupwise(x); c["fp8_1x128"] = [sha(q), sha(s)]
         q, s = O.quant_fp8_block(x); c["fp8_128x128"] = [sha(q), sha(s)]
         q, sf, gs = O.quant_nvfp4(x); c["nvfp4"] = [sha(q), sha(sf), float(gs), sha(O.swizzle_sf(sf)), q[0, :8].tolist(), sf[0, :4].tolist()]
+        q, sf, gs = O.quant_nvfp4(x, "per_token"); c["nvfp4_per_token"] = [sha(q), sha(sf), sha(gs), q[0, :8].tolist(), sf[0, :4].tolist(), float(gs[0]), float(gs[1])]
         q, sf = O.quant_mxfp4(x); c["mxfp4"] = [sha(q), sha(sf), sha(O.swizzle_sf(sf)), q[0, :8].tolist(), sf[0, :4].tolist()]
         q, s = O.quant_fp4_ref32(x); c["ref32_lut"] = [sha(q), sha(s)]
         cases[name] = c

@@ -149,6 +149,29 @@ def test_nvfp4_calibrated_activation_scale_is_one_pass_and_exact(cuda_device, gs
     assert torch.equal(got, linear(a.cuda(), pw, out_dtype="float32", act_global_scale=torch.tensor([gs], device="cuda")))
 
 
+@pytest.mark.parametrize("M", [3, 100, 600])
+def test_nvfp4_per_token_activation_scales_through_linear(cuda_device, M):
+    """`linear(..., act_global_scale="per_token")` (decode, 1-CTA and CTA-pair kernels): the product equals the oracle's
+    with per-token scales - (sum * weight global scale) * token scale - and the two-call form gives the same bits."""
+    from dsl_tool_b200 import pack_weight, quantize_fp4
+    from dsl_tool_b200.gemm_kernels import gemm_fp4_quantized, linear
+    rng = np.random.default_rng(92 + M)
+    N, K = 384, 1024
+    a = torch.from_numpy(activations(rng, M, K, outliers=True) * rng.uniform(0.01, 30, (M, 1)).astype(np.float32)).bfloat16()
+    w = torch.from_numpy(weights(rng, N, K)).bfloat16()
+    pw = pack_weight(w.cuda(), "nvfp4")
+    got = linear(a.cuda(), pw, out_dtype="float32", act_global_scale="per_token")
+    _status_ok()
+    pa, sfa, gsa = O.quant_nvfp4(a.float().numpy(), "per_token")
+    pb, sfb, gsb = O.quant_nvfp4(w.float().numpy())
+    assert rel_frobenius(got.cpu().numpy(), O.gemm_nvfp4(pa, sfa, gsa, pb, sfb, gsb)) <= REL_FROB_TOL
+    q, sf, gs = quantize_fp4(a.cuda(), "nvfp4", global_scale="per_token")
+    two = gemm_fp4_quantized(q, pw.q, sf, pw.scale, format="nvfp4", n=N, token_scale=gs, global_scale_b=pw.global_scale)
+    assert torch.equal(two, got)
+    with pytest.raises(ValueError, match="row_scale"):
+        linear(a.cuda(), pw, act_global_scale="per_token", row_scale=torch.ones(M, device="cuda"))
+
+
 def test_epilogue_row_and_column_rescale(cuda_device):
     from dsl_tool_b200.gemm_kernels import gemm_fp8_quantized
     rng = np.random.default_rng(5)

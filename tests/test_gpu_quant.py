@@ -96,6 +96,36 @@ def test_input_that_is_only_16_byte_aligned(cuda_device, dtype):
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 32), (7, 96), (129, 1056), (300, 4096), (40, 8192), (9, 28672)])
+def test_nvfp4_per_token_scales(cuda_device, shape, dtype):
+    """global_scale="per_token": one pass; bytes, scale tiles and the per-row global scales equal the oracle's (every
+    register-chunk count of the kernel: rows of 32 ... 28672 elements; an all-zero row gets scale 1 and zero bytes)."""
+    from dsl_tool_b200 import quantize_fp4
+    xc, xo = _inputs(shape, dtype, 21)
+    q, sf, gs = quantize_fp4(xc, "nvfp4", global_scale="per_token")
+    pq, psf, pgs = O.quant_nvfp4(xo, "per_token")
+    assert np.array_equal(gs.cpu().numpy(), pgs)
+    assert np.array_equal(q.cpu().numpy(), pq)
+    assert np.array_equal(O.unswizzle_sf(sf.cpu().numpy(), shape[0], shape[1] // 16), psf)
+    assert np.array_equal(sf.cpu().numpy(), O.swizzle_sf(psf))          # padding bytes are zero
+
+
+def test_nvfp4_per_token_ragged_groups_and_limits(cuda_device):
+    from dsl_tool_b200 import quantize_fp4
+    xc, xo = _inputs((300, 512), torch.bfloat16, 22)
+    offs = np.array([0, 5, 5, 140, 300], np.int32)
+    q, sf, gs = quantize_fp4(xc, "nvfp4", global_scale="per_token", group_offsets=torch.from_numpy(offs).cuda())
+    pq, psf, pgs = O.quant_nvfp4(xo, "per_token")
+    assert np.array_equal(gs.cpu().numpy(), pgs) and np.array_equal(q.cpu().numpy(), pq)
+    want = O.swizzle_sf_grouped(psf, offs)
+    assert np.array_equal(sf.cpu().numpy()[: want.size], want)
+    with pytest.raises(ValueError, match="at most"):
+        quantize_fp4(torch.zeros(2, 32768 + 32, device="cuda"), "nvfp4", global_scale="per_token")
+    with pytest.raises(ValueError, match="per_token"):
+        quantize_fp4(xc, "mxfp4", global_scale="per_token")
+
+
 def test_nvfp4_given_global_scale_and_zero_tensor(cuda_device):
     from dsl_tool_b200 import quantize_fp4
     xc, xo = _inputs((64, 128), torch.bfloat16, 4)

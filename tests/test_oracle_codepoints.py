@@ -103,6 +103,11 @@ def test_oracle_known_answers():
         q, s = O.quant_fp8_block(x); assert [sha(q), sha(s)] == c["fp8_128x128"]
         q, sf, gs = O.quant_nvfp4(x)
         assert [sha(q), sha(sf), float(gs), sha(O.swizzle_sf(sf)), q[0, :8].tolist(), sf[0, :4].tolist()] == c["nvfp4"]
+        q, sf, gs = O.quant_nvfp4(x, "per_token")
+        assert [sha(q), sha(sf), sha(gs), q[0, :8].tolist(), sf[0, :4].tolist(), float(gs[0]), float(gs[1])] == c["nvfp4_per_token"]
+        for m in (0, 1, m - 1):                  # the per-token rule is the tensor rule applied to each row alone
+            q1, sf1, g1 = O.quant_nvfp4(x[m:m + 1])
+            assert (q1[0] == q[m]).all() and (sf1[0] == sf[m]).all() and g1 == gs[m]
         q, sf = O.quant_mxfp4(x)
         assert [sha(q), sha(sf), sha(O.swizzle_sf(sf)), q[0, :8].tolist(), sf[0, :4].tolist()] == c["mxfp4"]
         q, s = O.quant_fp4_ref32(x); assert [sha(q), sha(s)] == c["ref32_lut"]
