@@ -137,6 +137,10 @@ struct Chunk16 {
         }
         return make_uint2(w[0], w[1]);
     }
+    __device__ __forceinline__ void to_float(float (&o)[16]) const {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = v[i];
+    }
 };
 template <>
 struct Chunk16<__nv_bfloat16> {
@@ -153,14 +157,16 @@ struct Chunk16<__nv_bfloat16> {
             w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
         }
     }
+    // max(|a|, |b|) per half with the signs xor-ed into the result: the magnitude is what the next step looks at, so
+    // the eight words chain without masking the signs first (a NaN half yields the other operand, as fmaxf does)
+    static __device__ __forceinline__ uint32_t absmax2(uint32_t a, uint32_t b) {
+        uint32_t d;
+        asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+        return d;
+    }
     __device__ __forceinline__ float amax() const {
-        uint32_t m = w[0] & 0x7FFF7FFFu;
-#pragma unroll
-        for (int i = 1; i < 8; ++i) {
-            const uint32_t a = w[i] & 0x7FFF7FFFu;
-            const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&m), *reinterpret_cast<const __nv_bfloat162*>(&a));
-            m = *reinterpret_cast<const uint32_t*>(&r);
-        }
+        const uint32_t m = absmax2(absmax2(absmax2(w[0], w[1]), absmax2(w[2], w[3])),
+                                   absmax2(absmax2(w[4], w[5]), absmax2(w[6], w[7]))) & 0x7FFF7FFFu;
         return fmaxf(__uint_as_float(m << 16), __uint_as_float(m & 0xFFFF0000u));
     }
     __device__ __forceinline__ uint2 quant_e2m1(float inv) const {
@@ -174,6 +180,13 @@ struct Chunk16<__nv_bfloat16> {
             b[i] = cvt_e2m1x2(lo, hi);
         }
         return make_uint2(pack4(b[0], b[1], b[2], b[3]), pack4(b[4], b[5], b[6], b[7]));
+    }
+    __device__ __forceinline__ void to_float(float (&o)[16]) const {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            o[2 * i] = __uint_as_float(w[i] << 16);
+            o[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
     }
 };
 
@@ -189,8 +202,14 @@ __device__ __forceinline__ float amax16(const float (&v)[16]) {
     for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
     return m;
 }
+// max(amax / 448, 1e-12).  The division is RN(amax * RN(1/448)) plus one residual correction, which equals the IEEE
+// quotient for every amax from 2^-100 up (checked exhaustively on the CPU: oracle/quotient_check.c, mode 4); below that
+// both are far under 1e-12, and an infinite amax (its residual would be NaN) keeps the infinite first product.
 __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
-    float s = __fdiv_rn(amax, 448.0f);
+    constexpr float r448 = 0x1.24924ap-9f;                                   // RN(1/448)
+    const float q0 = __fmul_rn(amax, r448);
+    float s = __fmaf_rn(__fmaf_rn(-q0, 448.0f, amax), r448, q0);
+    s = q0 > 3.0e38f ? q0 : s;
     return s < 1e-12f ? 1e-12f : s;
 }
 // x / s for the E4M3 conversion without a division per element.  With y = RN(1/s) shared by the
@@ -203,31 +222,41 @@ __device__ __forceinline__ float fp8_scale_from_amax(float amax) {
 // Scales the library derives are never smaller; a caller-given scale can be (its reciprocal may even
 // overflow), so quant16_e4m3 takes this path only for scales inside [1e-12, 3e38] and divides for
 // real otherwise.
-// Two values of q0 must pass through untouched: a zero (the zero residual is +0 and would turn -0
-// into +0) and an infinity (Inf - Inf poisons the residual); both are the fixed points of q -> 2q.
-// A NaN stays a NaN through the corrections.  Six FMA-pipe instructions, one compare and one select
-// per element instead of a reciprocal and range checks (half that with the packed instructions below).
+// Two values of q0 need care: a zero (the zero residual is +0 and would turn -0 into +0) and an infinity (Inf - Inf
+// poisons the residual).  With a scale DERIVED from the maximum of the very elements being divided, |x / s| <= 448 and
+// x is never infinite next to a finite scale, so only the zero remains, and since s > 0 the quotient simply takes the
+// sign of x (one logic instruction per element; GIVEN = false).  With a scale the caller GIVES, x * y can overflow,
+// and both are caught as the fixed points of q -> 2q (GIVEN = true).  A NaN stays a NaN through the corrections.
 // Written for two elements at a time with the packed fp32 instructions (mul / fma / add .f32x2: each half is the
 // IEEE operation of the scalar form q0 = x*y, q1 = fma(fma(-q0, s, x), y, q0), q2 likewise from q1, and
 // fma(-q, s, x) == fma(q, -s, x) bit for bit), which halves the instruction count of the E4M3 quantisers - they run
 // close to the issue limit.
+template <bool GIVEN>
 __device__ __forceinline__ void div2_for_e4m3(float x0, float x1, unsigned long long neg_s2, unsigned long long inv2, float& r0,
                                               float& r1) {
-    unsigned long long x, q0, q1, q2, r, d;
+    unsigned long long x, q0, q1, q2, r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(x0), "f"(x1));
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q0) : "l"(x), "l"(inv2));
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(q0), "l"(neg_s2), "l"(x));
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q1) : "l"(r), "l"(inv2), "l"(q0));
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(q1), "l"(neg_s2), "l"(x));
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q2) : "l"(r), "l"(inv2), "l"(q1));
-    asm("add.rn.f32x2 %0, %1, %1;" : "=l"(d) : "l"(q0));
-    float a0, a1, b0, b1, d0, d1;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(q0));
+    float b0, b1;
     asm("mov.b64 {%0, %1}, %2;" : "=f"(b0), "=f"(b1) : "l"(q2));
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
-    r0 = d0 == a0 ? a0 : b0;
-    r1 = d1 == a1 ? a1 : b1;
+    if (GIVEN) {
+        unsigned long long d;
+        asm("add.rn.f32x2 %0, %1, %1;" : "=l"(d) : "l"(q0));
+        float a0, a1, d0, d1;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(q0));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+        r0 = d0 == a0 ? a0 : b0;
+        r1 = d1 == a1 ? a1 : b1;
+    } else {
+        r0 = __uint_as_float((__float_as_uint(b0) & 0x7FFFFFFFu) | (__float_as_uint(x0) & 0x80000000u));
+        r1 = __uint_as_float((__float_as_uint(b1) & 0x7FFFFFFFu) | (__float_as_uint(x1) & 0x80000000u));
+    }
 }
+template <bool GIVEN>
 __device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
     uint32_t w[4];
     if (s >= 1e-12f && s <= 3.0e38f) {
@@ -239,9 +268,9 @@ __device__ __forceinline__ uint4 quant16_e4m3(const float (&v)[16], float s) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float a, b, c, d;
-            div2_for_e4m3(v[4 * i], v[4 * i + 1], neg_s2, inv2, a, b);
-            div2_for_e4m3(v[4 * i + 2], v[4 * i + 3], neg_s2, inv2, c, d);
-            w[i] = static_cast<uint32_t>(cvt_e4m3x2(a, b)) | (static_cast<uint32_t>(cvt_e4m3x2(c, d)) << 16);
+            div2_for_e4m3<GIVEN>(v[4 * i], v[4 * i + 1], neg_s2, inv2, a, b);
+            div2_for_e4m3<GIVEN>(v[4 * i + 2], v[4 * i + 3], neg_s2, inv2, c, d);
+            w[i] = __byte_perm(cvt_e4m3x2(a, b), cvt_e4m3x2(c, d), 0x5410);
         }
     } else {   // an infinite scale (an Inf among the inputs: 0 * Inf would poison the residual), or a given
                // scale too small for the residual argument above (also zero, negative, NaN): divide for real
@@ -332,7 +361,7 @@ quant_fp8_tensor_kernel(const T* __restrict__ x, size_t n, const uint32_t* amax_
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
         float v[16];
         load16<T>(x + i * 16, v);
-        *reinterpret_cast<uint4*>(q + i * 16) = quant16_e4m3(v, s);
+        *reinterpret_cast<uint4*>(q + i * 16) = amax_bits != nullptr ? quant16_e4m3<false>(v, s) : quant16_e4m3<true>(v, s);
     }
     if (blockIdx.x == 0 && threadIdx.x == 0)
         for (size_t i = nvec * 16; i < n; ++i)
@@ -350,18 +379,18 @@ quant_fp8_1x128_kernel(const T* __restrict__ x, long long M, int K, uint8_t* __r
     const long long row = blockIdx.x * static_cast<long long>(256 >> log2_cp) + (threadIdx.x >> log2_cp);
     const int kc = blockIdx.y * 256 + (threadIdx.x & ((1 << log2_cp) - 1));
     const bool valid = row < M && kc < cpr;
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = 0.f;
     const size_t off = static_cast<size_t>(row) * K + static_cast<size_t>(kc) * 16;
-    if (valid) load16w<T>(x + off, v, wide);
-    float m = amax16(v);   // the 8 lanes of a group are adjacent (slots per row are a multiple of 8)
+    Chunk16<T> ch;
+    if (valid) ch.load(x + off, wide); else ch.zero();
+    float m = ch.amax();   // the 8 lanes of a group are adjacent (slots per row are a multiple of 8)
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
     m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
     const float s = fp8_scale_from_amax(m);
     if (valid) {
-        *reinterpret_cast<uint4*>(q + off) = quant16_e4m3(v, s);
+        float v[16];
+        ch.to_float(v);
+        *reinterpret_cast<uint4*>(q + off) = quant16_e4m3<false>(v, s);
         if ((kc & 7) == 0) scales[static_cast<size_t>(row) * ng + (kc >> 3)] = s;
     }
 }
@@ -396,72 +425,126 @@ quant_fp8_block128_kernel(const T* __restrict__ w, int N, int K, uint8_t* __rest
 #pragma unroll
     for (int c = 0; c < 4; ++c)
         if (r < N && k0 + c * 16 < K)
-            *reinterpret_cast<uint4*>(q + static_cast<size_t>(r) * K + k0 + c * 16) = quant16_e4m3(v[c], s);
+            *reinterpret_cast<uint4*>(q + static_cast<size_t>(r) * K + k0 + c * 16) = quant16_e4m3<false>(v[c], s);
 }
 
 // ---- FP4 ---------------------------------------------------------------------------------
 constexpr int kMaxGroups = 1024;
 
-// Where the scale byte of (row, K-block) goes.  With ragged row groups every group starts at
-// a fresh 128-row tile (tile index = number of 128-row tiles of the groups before it).
+// Block scale of one NVFP4 chunk: byte = ue4m3(min((amax16 / 6) / gs, 448)), inv = 1 / (f32(byte) * gs), 0 when that
+// product is below FLT_MIN.  The two IEEE divisions are done without dividing: m / 6 as RN(m * RN(1/6)) plus one
+// residual correction (exhaustively equal to the division for every m >= 2^-100), a / gs with the reciprocal of gs
+// (computed once per thread) and two corrections (Markstein: correctly rounded).  Residuals are exact unless they
+// underflow; with gs inside [2^-64, 2^64] that needs a quotient below 2^-36, far under the smallest rounding boundary of
+// the scale byte (2^-10), where both forms give byte 0.  An infinite m turns into NaN and fminf returns 448 for it, as
+// it does for the infinite quotient.  Other global scales (a caller may give anything) take the real divisions.
+struct Nvfp4Scaler {
+    float gs, rgs;
+    bool fast;
+    __device__ __forceinline__ void init(float g) {
+        gs = g;
+        fast = g >= 0x1p-64f && g <= 0x1p64f;
+        rgs = fast ? __frcp_rn(g) : 0.f;
+    }
+    __device__ __forceinline__ uint32_t operator()(float m, float& inv) const {
+        float t;
+        if (fast) {
+            constexpr float r6 = 0x1.555556p-3f;                           // RN(1/6)
+            const float a0 = __fmul_rn(m, r6);
+            const float a = __fmaf_rn(__fmaf_rn(-a0, 6.0f, m), r6, a0);      // m / 6
+            const float q0 = __fmul_rn(a, rgs);
+            const float q1 = __fmaf_rn(__fmaf_rn(-q0, gs, a), rgs, q0);
+            t = __fmaf_rn(__fmaf_rn(-q1, gs, a), rgs, q1);                   // a / gs
+        } else {
+            t = __fdiv_rn(__fdiv_rn(m, 6.0f), gs);
+        }
+        t = fminf(t, 448.0f);
+        const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
+        const float d = __fmul_rn(e4m3_to_float(sfb), gs);
+        inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+        return sfb;
+    }
+};
+
+// Where the scale bytes of a row go.  With ragged row groups every group starts at a fresh 128-row tile (tile index =
+// number of 128-row tiles of the groups before it).  The kernels visit rows in ascending or descending order, so the
+// group of a row is found by stepping a cursor from the previous row's group (the table is monotone after
+// monotone_rows) instead of a binary search per row.
 struct SfIndexer {
     const int* offs;   // shared-memory copy of the group offsets [G+1], or nullptr
     const int* tile0;  // shared-memory first tile of each group [G+1]
     int groups;
     int katoms;
-    __device__ __forceinline__ size_t operator()(long long row, int blk) const {
-        long long tile;
-        int rin;
+    int g;             // cursor
+    // Byte offset of K-block 0 of `row`, or -1 for a row in front of the first group (it belongs to no group).
+    // K-block b of the row is (b >> 2) * 512 + (b & 3) bytes further on.
+    __device__ __forceinline__ long long row_base(unsigned row) {
+        unsigned tile, rin;
         if (offs == nullptr) {
             tile = row >> 7;
-            rin = static_cast<int>(row & 127);
+            rin = row & 127u;
         } else {
-            int lo = 0, hi = groups;   // last g with offs[g] <= row
-            while (hi - lo > 1) {
-                int mid = (lo + hi) >> 1;
-                if (offs[mid] <= row) lo = mid; else hi = mid;
-            }
-            int rl = static_cast<int>(row - offs[lo]);
-            tile = tile0[lo] + (rl >> 7);
-            rin = rl & 127;
+            const int r = static_cast<int>(row);
+            while (g + 1 < groups && r >= offs[g + 1]) ++g;
+            while (g > 0 && r < offs[g]) --g;
+            const int rl = r - offs[g];
+            if (rl < 0) return -1;
+            tile = static_cast<unsigned>(tile0[g] + (rl >> 7));
+            rin = static_cast<unsigned>(rl) & 127u;
         }
-        return (static_cast<size_t>(tile) * katoms + (blk >> 2)) * 512 + (rin & 31) * 16 + (rin >> 5) * 4 + (blk & 3);
+        return static_cast<long long>(static_cast<size_t>(tile) * katoms * 512 + (rin & 31u) * 16 + (rin >> 5) * 4);
     }
 };
 
-template <typename T, int FMT>   // FMT 0: NVFP4 (block 16, UE4M3 + global scale)  1: MXFP4 (block 32, E8M0)
-__global__ void __launch_bounds__(256)
-quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict__ gs_ptr,
-                 const uint32_t* __restrict__ amax_bits, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
-                 int num_groups, int log2_cp, bool wide) {
-    griddep_launch_dependents();   // a GEMM that opted in may set itself up (and stream its weight) from now on
-    __shared__ int s_offs[kMaxGroups + 1];
-    __shared__ int s_tile0[kMaxGroups + 1];
-    SfIndexer sfi;
-    const int nblk = FMT == 0 ? K / 16 : K / 32;
+// All threads: fills the shared tables from the (untrusted, device-resident) group offsets, sanitised exactly as the
+// GEMM kernels do, so that both derive the same scale tiles.  Contains two __syncthreads() when offsets are given.
+__device__ __forceinline__ void sf_indexer_init(SfIndexer& sfi, int* s_offs, int* s_tile0, const int* group_offsets,
+                                                int num_groups, int m_total, int nblk, bool from_the_end) {
     sfi.katoms = (nblk + 3) / 4;
     sfi.groups = num_groups;
     sfi.offs = nullptr;
     sfi.tile0 = nullptr;
-    if (group_offsets != nullptr) {
-        // untrusted device data: sanitised exactly as the GEMM kernels do, so both derive the same scale tiles
-        load_group_offsets(s_offs, group_offsets, num_groups, static_cast<int>(M));
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int t = 0;
-            for (int g = 0; g < num_groups; ++g) {
-                s_tile0[g] = t;
-                t += (monotone_rows(s_offs, g) + 127) >> 7;
-            }
-            s_tile0[num_groups] = t;
+    sfi.g = 0;
+    if (group_offsets == nullptr) return;
+    load_group_offsets(s_offs, group_offsets, num_groups, m_total);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int g = 0; g < num_groups; ++g) {
+            s_tile0[g] = t;
+            t += (monotone_rows(s_offs, g) + 127) >> 7;
         }
-        __syncthreads();
-        sfi.offs = s_offs;
-        sfi.tile0 = s_tile0;
+        s_tile0[num_groups] = t;
     }
+    __syncthreads();
+    sfi.offs = s_offs;
+    sfi.tile0 = s_tile0;
+    sfi.g = from_the_end ? num_groups - 1 : 0;
+}
+
+// One thread per 16-element chunk; a block of 256 threads covers 2^(8 - log2_cp) rows x 2^log2_cp chunk slots and walks the
+// row blocks grid-stride.  Everything that depends only on the thread's column (pointers, scale-tile column, writer role)
+// is set up once; per row block there is one 32 x 32 -> 64 bit multiply for the addresses.  These kernels are bound by
+// instruction issue as much as by DRAM (ncu: issue slots 81 % busy at 52 % of the DRAM peak before this form), so
+// instructions per chunk are what counts.
+template <typename T, int FMT>   // FMT 0: NVFP4 (block 16, UE4M3 + global scale)  1: MXFP4 (block 32, E8M0)
+__global__ void __launch_bounds__(256)
+quant_fp4_kernel(const T* __restrict__ x, unsigned M, int K, float* __restrict__ gs_ptr,
+                 const uint32_t* __restrict__ amax_bits, uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
+                 int num_groups, int log2_cp, unsigned row_blocks, bool wide) {
+    griddep_launch_dependents();   // a GEMM that opted in may set itself up (and stream its weight) from now on
+    __shared__ int s_offs[kMaxGroups + 1];
+    __shared__ int s_tile0[kMaxGroups + 1];
+    // After an amax pass the END of the tensor is what the L2 still holds (that pass walks it front to
+    // back), so this pass then walks the row blocks back to front and finds much of its input there.
+    const bool backwards = FMT == 0 && amax_bits != nullptr;
+    SfIndexer sfi;
+    sf_indexer_init(sfi, s_offs, s_tile0, group_offsets, num_groups, static_cast<int>(M > 0x7FFFFFFFu ? 0x7FFFFFFFu : M),
+                    FMT == 0 ? K / 16 : K / 32, backwards);
     // NVFP4 global scale: given (gs_ptr holds it) or derived here from the tensor amax and published
-    float gs = 1.0f;
+    Nvfp4Scaler scaler;
     if (FMT == 0) {
+        float gs;
         if (amax_bits != nullptr) {
             const float a = __uint_as_float(*amax_bits);
             gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
@@ -469,60 +552,57 @@ quant_fp4_kernel(const T* __restrict__ x, long long M, int K, float* __restrict_
         } else {
             gs = *gs_ptr;
         }
+        scaler.init(gs);
     }
-    const int cpr = K / 16;   // 16-element chunks per row
-    const int rpb = 256 >> log2_cp;
-    const long long row_blocks = (M + rpb - 1) / rpb;
+    const int cpr = K >> 4;   // 16-element chunks per row
     const int kc = blockIdx.y * 256 + (threadIdx.x & ((1 << log2_cp) - 1));
-    // grid-stride over row blocks: the group tables above are built once per CTA, not once per row.
-    // After an amax pass the END of the tensor is what the L2 still holds (that pass walks it front to
-    // back), so this pass then walks the row blocks back to front and finds much of its input there.
-    const bool backwards = FMT == 0 && amax_bits != nullptr;
-    for (long long it = blockIdx.x; it < row_blocks; it += gridDim.x) {
-    const long long rb = backwards ? row_blocks - 1 - it : it;
-    const long long row = rb * rpb + (threadIdx.x >> log2_cp);
-    const bool valid = row < M && kc < cpr;
-    const size_t id = static_cast<size_t>(row) * cpr + kc;
-    Chunk16<T> ch;
-    ch.zero();
-    if (valid) ch.load(x + id * 16, wide);
-    float m = ch.amax();
-    float inv;
-    uint32_t sfb;
-    int blk;
-    bool writer;
-    if (FMT == 0) {
-        float t = __fdiv_rn(__fdiv_rn(m, 6.0f), gs);
-        t = fminf(t, 448.0f);
-        sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
-        const float d = __fmul_rn(e4m3_to_float(sfb), gs);
-        inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
-        blk = kc;
-        writer = true;
-    } else {
-        m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));   // cpr is even, so lane pairs share a row
-        int e = static_cast<int>((__float_as_uint(m) >> 23) & 0xFFu) - 129;
-        e = e < -127 ? -127 : e;
-        sfb = static_cast<uint32_t>(e + 127);
-        inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-        blk = kc >> 1;
-        writer = (kc & 1) == 0;
-    }
-    if (valid) *reinterpret_cast<uint2*>(q + id * 8) = ch.quant_e2m1(inv);
+    const unsigned rsub = threadIdx.x >> log2_cp;
+    const int rpb_log2 = 8 - log2_cp;
+    const bool col_ok = kc < cpr;
+    const size_t pitch_x = static_cast<size_t>(K) * sizeof(T);
+    const size_t pitch_q = static_cast<size_t>(K >> 1);
+    const uint8_t* xcol = reinterpret_cast<const uint8_t*>(x) + static_cast<size_t>(kc) * (16 * sizeof(T));
+    uint8_t* qcol = q + static_cast<size_t>(kc) * 8;
     // Scale bytes: four consecutive K-blocks of a row are four consecutive bytes of the tile
     // layout, so when the row length allows it one lane stores all four as a word.
     constexpr int LANES_PER_BLK = FMT == 0 ? 1 : 2;
+    const int blk = FMT == 0 ? kc : kc >> 1;
     const bool packed = (cpr % (4 * LANES_PER_BLK)) == 0;   // uniform over the grid
-    if (packed) {
-        uint32_t word = sfb;
-        word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 1 * LANES_PER_BLK) << 8;
-        word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 2 * LANES_PER_BLK) << 16;
-        word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 3 * LANES_PER_BLK) << 24;
-        if (valid && (kc % (4 * LANES_PER_BLK)) == 0)
-            *reinterpret_cast<uint32_t*>(sf + sfi(row, blk)) = word;
-    } else if (valid && writer) {
-        sf[sfi(row, blk)] = static_cast<uint8_t>(sfb);
-    }
+    const bool sf_writer = col_ok && (packed ? (kc % (4 * LANES_PER_BLK)) == 0 : (FMT == 0 || (kc & 1) == 0));
+    uint8_t* sfcol = sf + static_cast<size_t>(blk >> 2) * 512 + (blk & 3);
+    for (unsigned it = blockIdx.x; it < row_blocks; it += gridDim.x) {
+        const unsigned rb = backwards ? row_blocks - 1 - it : it;
+        const unsigned row = (rb << rpb_log2) + rsub;
+        const bool valid = col_ok && row < M;
+        Chunk16<T> ch;
+        if (valid) ch.load(reinterpret_cast<const T*>(xcol + row * pitch_x), wide); else ch.zero();
+        float m = ch.amax();
+        float inv;
+        uint32_t sfb;
+        if (FMT == 0) {
+            sfb = scaler(m, inv);
+        } else {
+            m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));   // cpr is even, so lane pairs share a row
+            int e = static_cast<int>((__float_as_uint(m) >> 23) & 0xFFu) - 129;
+            e = e < -127 ? -127 : e;
+            sfb = static_cast<uint32_t>(e + 127);
+            inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+        }
+        if (valid) *reinterpret_cast<uint2*>(qcol + row * pitch_q) = ch.quant_e2m1(inv);
+        if (packed) {
+            uint32_t word = sfb;
+            word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 1 * LANES_PER_BLK) << 8;
+            word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 2 * LANES_PER_BLK) << 16;
+            word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 3 * LANES_PER_BLK) << 24;
+            sfb = word;
+        }
+        if (sf_writer && row < M) {
+            const long long base = sfi.row_base(row);
+            if (base >= 0) {
+                if (packed) *reinterpret_cast<uint32_t*>(sfcol + base) = sfb;
+                else sfcol[base] = static_cast<uint8_t>(sfb);
+            }
+        }
     }
 }
 
@@ -539,27 +619,9 @@ quant_nvfp4_token_kernel(const T* __restrict__ x, long long M, int K, float* __r
     __shared__ int s_offs[kMaxGroups + 1];
     __shared__ int s_tile0[kMaxGroups + 1];
     __shared__ float red[2][ROWS][8];
-    SfIndexer sfi;
     const int cpr = K / 16;
-    sfi.katoms = (cpr + 3) / 4;
-    sfi.groups = num_groups;
-    sfi.offs = nullptr;
-    sfi.tile0 = nullptr;
-    if (group_offsets != nullptr) {
-        load_group_offsets(s_offs, group_offsets, num_groups, static_cast<int>(M));
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int t = 0;
-            for (int g = 0; g < num_groups; ++g) {
-                s_tile0[g] = t;
-                t += (monotone_rows(s_offs, g) + 127) >> 7;
-            }
-            s_tile0[num_groups] = t;
-        }
-        __syncthreads();
-        sfi.offs = s_offs;
-        sfi.tile0 = s_tile0;
-    }
+    SfIndexer sfi;
+    sf_indexer_init(sfi, s_offs, s_tile0, group_offsets, num_groups, static_cast<int>(M), cpr, false);
     const bool packed = (cpr % 4) == 0;     // four consecutive K-blocks of a row are one word of the tile layout
     const long long row_groups = (M + ROWS - 1) / ROWS;
     int it = 0;
@@ -574,8 +636,8 @@ quant_nvfp4_token_kernel(const T* __restrict__ x, long long M, int K, float* __r
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int kc = threadIdx.x + r * 256;
-                ch[j][r].zero();
                 if (row0 + j < M && kc < cpr) ch[j][r].load(x + (static_cast<size_t>(row0 + j) * cpr + kc) * 16, wide);
+                else ch[j][r].zero();
             }
         }
 #pragma unroll
@@ -598,24 +660,26 @@ quant_nvfp4_token_kernel(const T* __restrict__ x, long long M, int K, float* __r
             for (int w = 1; w < 8; ++w) a = fmaxf(a, red[it & 1][j][w]);
             const float gs = a == 0.f ? 1.0f : __fdiv_rn(a, 2688.0f);
             if (threadIdx.x == 0 && row < M) gs_out[row] = gs;
+            Nvfp4Scaler scaler;
+            scaler.init(gs);
+            // rows come in ascending order (the cursor of the indexer relies on it); only the lanes that store need it
+            const long long base = row < M ? sfi.row_base(static_cast<unsigned>(row)) : -1;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int kc = threadIdx.x + r * 256;
                 const bool valid = row < M && kc < cpr;
-                float t = __fdiv_rn(__fdiv_rn(bm[j][r], 6.0f), gs);
-                t = fminf(t, 448.0f);
-                const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
-                const float d = __fmul_rn(e4m3_to_float(sfb), gs);
-                const float inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+                float inv;
+                uint32_t sfb = scaler(bm[j][r], inv);
                 if (valid) *reinterpret_cast<uint2*>(q + (static_cast<size_t>(row) * cpr + kc) * 8) = ch[j][r].quant_e2m1(inv);
+                uint8_t* dst = sf + base + static_cast<size_t>(kc >> 2) * 512 + (kc & 3);
                 if (packed) {
                     uint32_t word = sfb;
                     word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 1) << 8;
                     word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 2) << 16;
                     word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 3) << 24;
-                    if (valid && (kc & 3) == 0) *reinterpret_cast<uint32_t*>(sf + sfi(row, kc)) = word;
-                } else if (valid) {
-                    sf[sfi(row, kc)] = static_cast<uint8_t>(sfb);
+                    if (valid && base >= 0 && (kc & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
+                } else if (valid && base >= 0) {
+                    *dst = static_cast<uint8_t>(sfb);
                 }
             }
         }
@@ -650,17 +714,15 @@ quant_nvfp4_small_kernel(const T* __restrict__ x, int M, int K, float* __restric
         *gs_out = s_gs;
     }
     __syncthreads();
-    const float gs = s_gs;
+    Nvfp4Scaler scaler;
+    scaler.init(s_gs);
     const int katoms = (cpr + 3) / 4;
     for (int c = threadIdx.x; c < total; c += blockDim.x) {
         const int row = c / cpr, kc = c - row * cpr;
         float v[16];
         load16<T>(x + static_cast<size_t>(c) * 16, v);   // second read comes from L1/L2
-        float t = __fdiv_rn(__fdiv_rn(amax16(v), 6.0f), gs);
-        t = fminf(t, 448.0f);
-        const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
-        const float d = __fmul_rn(e4m3_to_float(sfb), gs);
-        const float inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+        float inv;
+        const uint32_t sfb = scaler(amax16(v), inv);
         *reinterpret_cast<uint2*>(q + static_cast<size_t>(c) * 8) = quant16_e2m1(v, inv);
         sf[(static_cast<size_t>(row >> 7) * katoms + (kc >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kc & 3)] =
             static_cast<uint8_t>(sfb);
@@ -723,20 +785,70 @@ quant_nvfp4_cluster_kernel(const T* __restrict__ x, int M, int K, float* __restr
     __syncthreads();
     // this CTA is done reading its peers; they may not exit before everyone has said so (waited for at the end)
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    const float gs = s_gs;
+    Nvfp4Scaler scaler;
+    scaler.init(s_gs);
     const int katoms = (cpr + 3) / 4;
     for (int c = gtid; c < total; c += kThreads) {
         const int row = c / cpr, kc = c - row * cpr;
         float v[16];
         load16<T>(x + static_cast<size_t>(c) * 16, v);
-        float t = __fdiv_rn(__fdiv_rn(amax16(v), 6.0f), gs);
-        t = fminf(t, 448.0f);
-        const uint32_t sfb = cvt_e4m3x2(t, 0.f) & 0xFFu;
-        const float d = __fmul_rn(e4m3_to_float(sfb), gs);
-        const float inv = d >= FLT_MIN ? __frcp_rn(d) : 0.f;
+        float inv;
+        const uint32_t sfb = scaler(amax16(v), inv);
         *reinterpret_cast<uint2*>(q + static_cast<size_t>(c) * 8) = quant16_e2m1(v, inv);
         sf[(static_cast<size_t>(row >> 7) * katoms + (kc >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (kc & 3)] =
             static_cast<uint8_t>(sfb);
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Per-tensor FP8 of a small tensor (up to 1 M elements, e.g. the 1024 x 1024 plumbing configuration) in ONE launch: the
+// same 8-CTA cluster scheme as above - every CTA reduces its share, the maxima meet through distributed shared memory,
+// the scale max(amax / 448, 1e-12) is published, and the second sweep (from L2) quantises - instead of memset + amax
+// kernel + quantise kernel, whose launch gaps are longer than their work at this size.  n % 16 == 0.
+template <typename T>
+__global__ void __cluster_dims__(kQuantClusterCtas, 1, 1) __launch_bounds__(1024)
+quant_fp8_tensor_cluster_kernel(const T* __restrict__ x, int nvec, float* __restrict__ scale_out, uint8_t* __restrict__ q) {
+    griddep_launch_dependents();
+    __shared__ float red[32];
+    __shared__ float s_cta_amax;
+    __shared__ float s_scale;
+    const uint32_t rank = cluster_ctarank();
+    const int gtid = static_cast<int>(rank) * 1024 + threadIdx.x;
+    constexpr int kThreads = kQuantClusterCtas * 1024;
+    float m = 0.f;
+    for (int c = gtid; c < nvec; c += kThreads) {
+        float v[16];
+        load16<T>(x + static_cast<size_t>(c) * 16, v);
+        m = fmaxf(m, amax16(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if (lane_id() == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float a = red[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        if (threadIdx.x == 0) s_cta_amax = a;
+    }
+    cluster_sync_all();
+    if (threadIdx.x < 32) {
+        float a = threadIdx.x < kQuantClusterCtas ? ld_cluster_f32(&s_cta_amax, threadIdx.x) : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, o));
+        if (threadIdx.x == 0) {
+            s_scale = fp8_scale_from_amax(a);
+            if (rank == 0) *scale_out = s_scale;
+        }
+    }
+    __syncthreads();
+    // this CTA is done reading its peers; they may not exit before everyone has said so (waited for at the end)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    const float s = s_scale;
+    for (int c = gtid; c < nvec; c += kThreads) {
+        float v[16];
+        load16<T>(x + static_cast<size_t>(c) * 16, v);
+        *reinterpret_cast<uint4*>(q + static_cast<size_t>(c) * 16) = quant16_e4m3<false>(v, s);
     }
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -770,6 +882,10 @@ static cudaError_t quant_fp8_typed(const T* x, long long rows, long long cols, i
     const size_t n = static_cast<size_t>(rows) * cols;
     // 256-bit loads need every 16-element chunk on a 32-byte boundary: base pointer and row pitch
     const bool wide = (reinterpret_cast<uintptr_t>(x) & 31u) == 0 && (static_cast<size_t>(cols) * sizeof(T)) % 32 == 0;
+    if (mode == DSL_FP8_PER_TENSOR && !scale_given && n % 16 == 0 && n >= (16u << 10) && n <= (1u << 20)) {
+        quant_fp8_tensor_cluster_kernel<T><<<kQuantClusterCtas, 1024, 0, st>>>(x, static_cast<int>(n / 16), scale_io, q);
+        return cudaGetLastError();
+    }
     if (mode == DSL_FP8_PER_TENSOR) {
         const int grid = grid_for(n / 16, 256, 148 * 16);
         if (!scale_given) {
@@ -828,13 +944,15 @@ static cudaError_t quant_fp4_typed(const T* x, long long rows, long long cols, i
     const uint32_t* amax_bits = (format == DSL_FP4_NV && !gs_given) ? ws : nullptr;
     const RowMap rm = make_row_map(cols, 1);
     dim3 grid = row_map_grid(rm, rows, cols);
+    const unsigned row_blocks = grid.x;
     const unsigned cap = 148u * 16u / (grid.y > 0 ? grid.y : 1u) + 1u;   // persistent: a few CTAs per SM
     if (grid.x > cap) grid.x = cap;
+    const unsigned m = static_cast<unsigned>(rows);                        // at most 2^31 (checked by the caller)
     if (grid.x > 0 && grid.y > 0) {
         if (format == DSL_FP4_NV)
-            quant_fp4_kernel<T, 0><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), gs_io, amax_bits, q, sf, group_offsets, num_groups, rm.log2_cp, wide);
+            quant_fp4_kernel<T, 0><<<grid, 256, 0, st>>>(x, m, static_cast<int>(cols), gs_io, amax_bits, q, sf, group_offsets, num_groups, rm.log2_cp, row_blocks, wide);
         else
-            quant_fp4_kernel<T, 1><<<grid, 256, 0, st>>>(x, rows, static_cast<int>(cols), nullptr, nullptr, q, sf, group_offsets, num_groups, rm.log2_cp, wide);
+            quant_fp4_kernel<T, 1><<<grid, 256, 0, st>>>(x, m, static_cast<int>(cols), nullptr, nullptr, q, sf, group_offsets, num_groups, rm.log2_cp, row_blocks, wide);
     }
     return cudaGetLastError();
 }

@@ -166,8 +166,10 @@ class MoEWeights:
         return MoEWeights(gu, dn, first, last, E, hidden_global_scale)
 
 
-def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True) -> torch.Tensor:
-    """This rank's share of the layer's result, fp32 [tokens, D]: the sum over the slots routed to its experts.
+def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
+                out_dtype=torch.float32) -> torch.Tensor:
+    """This rank's share of the layer's result, [tokens, D] (fp32, or bf16 = the fp32 sum rounded once, which saves
+    a conversion pass when the shares travel in bf16): the sum over the slots routed to its experts.
     NVFP4 / MXFP4 weights take the quantise-once path; with `hidden_global_scale` set (NVFP4) the hidden
     activation is quantised in the epilogue of the gate/up GEMM, otherwise it is written in bf16 and quantised
     by a separate pass (which, when the rank holds only part of the experts, reads the local row count back to
@@ -215,7 +217,7 @@ def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
         rows = dispatch_rows(p, x.to(torch.bfloat16), w.first, w.last)
         h = linear(rows, w.gate_up, expert_offsets=offs, activation="swiglu", out_dtype=torch.bfloat16)
         y = linear(h, w.down, expert_offsets=offs, out_dtype=torch.bfloat16)
-    return combine(p, y, w.first, w.last, out_dtype=torch.float32)
+    return combine(p, y, w.first, w.last, out_dtype=out_dtype)
 
 
 def pack_wire(p: MoEPlan, packed: torch.Tensor, sf: torch.Tensor, K: int, format: str) -> torch.Tensor:
@@ -335,8 +337,11 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
         return moe_forward_all_to_all(x, logits, w, k, renormalize=renormalize, out_dtype=out_dtype, group=group)
     if reduce not in ("all_reduce", "reduce_scatter"):
         raise ValueError("reduce must be 'all_reduce' or 'reduce_scatter'")
-    out = moe_partial(x, logits, w, k, renormalize=renormalize)
-    if (w.last - w.first) < w.experts:
+    partial = (w.last - w.first) < w.experts
+    # shares that travel in bf16 are written in bf16 by the combine itself (fp32 sum, one rounding)
+    direct = partial and exchange_dtype == torch.bfloat16
+    out = moe_partial(x, logits, w, k, renormalize=renormalize, out_dtype=torch.bfloat16 if direct else torch.float32)
+    if partial:
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized():
             raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")

@@ -178,8 +178,8 @@ def exchange_rows(records: torch.Tensor, counts_per_expert: torch.Tensor, expert
         return RowExchange([n], [n], counts_in, records[:n])
     counts_in_dev = torch.empty(world * local, dtype=torch.int32, device=records.device)
     dist.all_to_all_single(counts_in_dev, counts_per_expert, [local] * world, [l - f for f, l in ranges], group=group)
-    counts_host = counts_per_expert.cpu()
-    counts_in = counts_in_dev.cpu().view(world, local)
+    both = torch.cat([counts_per_expert, counts_in_dev]).cpu()          # the layer's one read-back
+    counts_host, counts_in = both[:experts], both[experts:].view(world, local)
     send_rows = [int(counts_host[f:l].sum()) for f, l in ranges]
     recv_rows = [int(v) for v in counts_in.sum(dim=1)]
     received = torch.empty((sum(recv_rows),) + tuple(records.shape[1:]), dtype=records.dtype, device=records.device)

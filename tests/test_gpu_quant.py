@@ -9,7 +9,7 @@ from tests.helpers import activations, weights
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16, torch.float16]
-SHAPES = [(1, 32), (7, 96), (128, 256), (129, 1056), (300, 512), (1024, 4096)]
+SHAPES = [(1, 32), (7, 96), (128, 256), (129, 1056), (300, 512), (1024, 1024), (1024, 4096)]
 
 
 def _inputs(shape, dtype, seed, outliers=True):
