@@ -84,6 +84,10 @@ WORKLOADS = {
     # the same layer with the tokens split over the ranks and a token all-to-all either side of the expert GEMMs
     "moe_layer_nvfp4_a2a": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
                                 hidden_gs=0.01, a2a=True),
+    # the replicated-routing layer in 2 pipelined pieces: each piece's reduce-scatter overlaps the next piece's GEMMs
+    # (measured slower than the unchunked layer on 2 and 4 GPUs, so it is not part of the sweep; --workload runs it)
+    "moe_layer_nvfp4_overlap": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
+                                    hidden_gs=0.01, chunks=2),
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
 }
 DEFAULT_WORKLOAD = "fp8_groupwise_llama8b_mlp"
@@ -259,6 +263,7 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
     from dsl_tool_b200 import MoEWeights, moe_forward
     T, E, k, K, H, D = cfg["tokens"], cfg["experts"], cfg["topk"], cfg["K"], cfg["H"], cfg["D"]
     a2a = bool(cfg.get("a2a")) and strong and world > 1
+    chunks = int(cfg.get("chunks", 1)) if strong and world > 1 else 1
     mine = slice(rank * (T // world), (rank + 1) * (T // world)) if a2a else slice(0, T)
     acts, logits, wts = [], [], []
     for s in range(sets):
@@ -278,7 +283,7 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
                                dispatch="all_to_all")
         # expert-parallel ranks exchange bf16 partial results and keep their own token rows (reduce-scatter)
         return moe_forward(acts[i % sets] if a is None else a, logits[i % sets], wts[i % sets], k, out_dtype=torch.bfloat16,
-                           reduce="reduce_scatter", exchange_dtype=torch.bfloat16)
+                           reduce="reduce_scatter", exchange_dtype=torch.bfloat16, chunks=chunks)
 
     flops = 2.0 * T * k * (2 * H * K + D * H) / (world if strong else 1)
     return dict(step=step, acts=acts, wts=wts, offs=None, M=T * k, K=K, N=2 * H, kind=cfg["kind"], flops=flops, moe=True,

@@ -120,15 +120,20 @@ def dispatch_rows(p: MoEPlan, x: torch.Tensor, first: int, last: int) -> torch.T
     return out
 
 
-def combine(p: MoEPlan, y: torch.Tensor, first: int, last: int, out_dtype=torch.float32) -> torch.Tensor:
+def combine(p: MoEPlan, y: torch.Tensor, first: int, last: int, out_dtype=torch.float32, out=None) -> torch.Tensor:
     """y [rows, D] (expert-sorted results of the local experts) -> [tokens, D]: weighted sum over each token's
-    local slots, in slot order."""
+    local slots, in slot order.  `out` (contiguous [tokens, D], float32 or bfloat16) receives the result when given."""
     dev = _lib.require_cuda(y)
     if y.dtype not in (torch.float32, torch.bfloat16):
         raise TypeError("y must be float32 or bfloat16")
     y = y.contiguous()
     T, k = p.ids.shape
-    out = torch.empty((T, y.shape[1]), dtype=out_dtype, device=dev)
+    if out is None:
+        out = torch.empty((T, y.shape[1]), dtype=out_dtype, device=dev)
+    elif out.shape != (T, y.shape[1]) or not out.is_contiguous() or out.device != y.device or \
+            out.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("out must be a contiguous [tokens, D] float32 / bfloat16 tensor on the device of y")
+    out_dtype = out.dtype
     with torch.cuda.device(dev):
         rc = _lib.lib().dsl_moe_combine(y.data_ptr(), _lib.dtype_code(y.dtype), p.ids.data_ptr(), p.dest.data_ptr(),
                                         p.offsets.data_ptr(), p.weights.data_ptr(), T, k, y.shape[1], first, last,
@@ -166,6 +171,26 @@ class MoEWeights:
         return MoEWeights(gu, dn, first, last, E, hidden_global_scale)
 
 
+def _experts_fp4(p: MoEPlan, packed: torch.Tensor, sf: torch.Tensor, gs, w: MoEWeights, K: int) -> torch.Tensor:
+    """Tokens quantised once (packed rows + scale tiles, NVFP4 / MXFP4) -> the local experts' results, expert-sorted
+    bf16 rows [tokens * k, D] (rows beyond the local total unwritten): dispatch, gate/up GEMM with SwiGLU, down GEMM."""
+    fmt = w.gate_up.format
+    offs = _local_offsets(p, w.first, w.last)
+    q_rows, sf_rows = dispatch_fp4(p, packed, sf, K, fmt, w.first, w.last)
+    common = dict(format=fmt, expert_offsets=offs, b_static=True)
+    if fmt == "nvfp4" and w.hidden_global_scale is not None:
+        hq, hsf, hgs = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
+                                          global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype="nvfp4",
+                                          out_global_scale=w.hidden_global_scale, **common)
+    else:
+        h = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
+                               global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype=torch.bfloat16, **common)
+        n_local = h.shape[0] if (w.last - w.first) == w.experts else int(offs[-1].item())
+        hq, hsf, hgs = quantize_fp4(h[:n_local], fmt, group_offsets=offs)
+    return gemm_fp4_quantized(hq, w.down.q, hsf, w.down.scale, n=w.down.n, global_scale_a=hgs,
+                              global_scale_b=w.down.global_scale, out_dtype=torch.bfloat16, **common)
+
+
 def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
                 out_dtype=torch.float32) -> torch.Tensor:
     """This rank's share of the layer's result, [tokens, D] (fp32, or bf16 = the fp32 sum rounded once, which saves
@@ -181,19 +206,7 @@ def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
     K = x.shape[1]
     if fmt in ("nvfp4", "mxfp4"):
         packed, sf, gs = quantize_fp4(x, fmt)
-        q_rows, sf_rows = dispatch_fp4(p, packed, sf, K, fmt, w.first, w.last)
-        common = dict(format=fmt, expert_offsets=offs, b_static=True)
-        if fmt == "nvfp4" and w.hidden_global_scale is not None:
-            hq, hsf, hgs = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
-                                              global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype="nvfp4",
-                                              out_global_scale=w.hidden_global_scale, **common)
-        else:
-            h = gemm_fp4_quantized(q_rows, w.gate_up.q, sf_rows, w.gate_up.scale, n=w.gate_up.n, global_scale_a=gs,
-                                   global_scale_b=w.gate_up.global_scale, activation="swiglu", out_dtype=torch.bfloat16, **common)
-            n_local = h.shape[0] if (w.last - w.first) == w.experts else int(offs[-1].item())
-            hq, hsf, hgs = quantize_fp4(h[:n_local], fmt, group_offsets=offs)
-        y = gemm_fp4_quantized(hq, w.down.q, hsf, w.down.scale, n=w.down.n, global_scale_a=hgs,
-                               global_scale_b=w.down.global_scale, out_dtype=torch.bfloat16, **common)
+        y = _experts_fp4(p, packed, sf, gs, w, K)
     elif fmt == "fp8":
         # per-tensor scale: taken over the tokens, so that it does not depend on which experts are local;
         # the E4M3 bytes are dispatched.  The hidden activation's scale is this rank's (valid rows only).
@@ -320,9 +333,58 @@ def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights,
     return combine(p, back, 0, w.experts, out_dtype=out_dtype)
 
 
+def _moe_forward_chunked(x, logits, w: MoEWeights, k: int, renormalize: bool, group, reduce: str, exchange_dtype,
+                         chunks: int) -> torch.Tensor:
+    """Expert-parallel layer (replicated routing, NVFP4 / MXFP4) in `chunks` pipelined pieces: routing and the activation
+    quantiser run once over all tokens (so the NVFP4 global scale is the whole tensor's, as without chunks), then every
+    piece is dispatched, multiplied and combined on the compute stream while the previous piece's partial results
+    are summed over the ranks by an asynchronous collective on NCCL's stream.  Returns the summed result in the exchange
+    dtype: all tokens (all_reduce) or this rank's token rows (reduce_scatter)."""
+    import torch.distributed as dist
+    fmt = w.gate_up.format
+    world = dist.get_world_size(group)
+    T, K = x.shape
+    D = w.down.n
+    dt = exchange_dtype if exchange_dtype is not None else torch.float32
+    if dt not in (torch.float32, torch.bfloat16):
+        raise ValueError("chunks > 1: the exchange dtype must be float32 or bfloat16")
+    scatter = reduce == "reduce_scatter"
+    piece = T // (world * chunks) if scatter else T // chunks        # token rows of one piece (per rank when scattering)
+    if piece * chunks * (world if scatter else 1) != T or piece % 128:
+        raise ValueError(f"chunks={chunks}: every piece must be a multiple of 128 token rows "
+                         f"(tokens {T}, ranks {world if scatter else 1})")
+    ids, wts = route(logits, k, renormalize)
+    packed, sf, gs = quantize_fp4(x, fmt)
+    nblk = K // 16 if fmt == "nvfp4" else K // 32
+    tile_bytes = ((nblk + 3) // 4) * 512                              # one 128-row scale tile row of the plain layout
+    outer = world if scatter else 1
+    # piece c = rows [c * piece, (c + 1) * piece) of every rank's token range: after the reduce-scatter rank r holds
+    # rows [c * piece, (c + 1) * piece) of ITS range, i.e. the pieces land side by side in the rank's result
+    packed_v = packed.view(outer, chunks, piece, K // 2)
+    sf_v = sf[:(T // 128) * tile_bytes].view(outer, chunks, piece // 128, tile_bytes)
+    ids_v = ids.view(outer, chunks, piece, k)
+    wts_v = wts.view(outer, chunks, piece, k)
+    out = torch.empty((piece * chunks, D), dtype=dt, device=x.device)
+    works, keep = [], []
+    for c in range(chunks):
+        p = plan(ids_v[:, c].reshape(outer * piece, k), wts_v[:, c].reshape(outer * piece, k), w.experts)
+        y = _experts_fp4(p, packed_v[:, c].reshape(outer * piece, K // 2), sf_v[:, c].reshape(-1), gs, w, K)
+        dst = out[c * piece:(c + 1) * piece]
+        if scatter:
+            part = combine(p, y, w.first, w.last, out_dtype=dt)
+            works.append(dist.reduce_scatter_tensor(dst, part, group=group, async_op=True))
+            keep.append(part)
+        else:
+            combine(p, y, w.first, w.last, out=dst)
+            works.append(dist.all_reduce(dst, group=group, async_op=True))
+    for wk in works:
+        wk.wait()
+    return out
+
+
 def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
                 out_dtype=torch.float32, group=None, reduce: str = "all_reduce", exchange_dtype=None,
-                dispatch: str = "replicated") -> torch.Tensor:
+                dispatch: str = "replicated", chunks: int = 1) -> torch.Tensor:
     """One MoE feed-forward layer: x [tokens, K], router logits [tokens, experts] -> [tokens, D].
     dispatch "all_to_all": x / logits are this rank's OWN token rows and the result is theirs
     (`moe_forward_all_to_all`); the remaining arguments below apply to "replicated".
@@ -330,7 +392,10 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
     default process group of torch.distributed): reduce "all_reduce" leaves the whole result on every rank,
     "reduce_scatter" leaves rank r with token rows [r * tokens / world, (r + 1) * tokens / world) - half the
     traffic, and what a sequence-sharded consumer wants.  `exchange_dtype` (e.g. torch.bfloat16) rounds the
-    partial results before they travel; default fp32."""
+    partial results before they travel; default fp32.  `chunks` > 1 (NVFP4 / MXFP4 weights, expert-parallel) runs the
+    layer in that many pieces so that each piece's collective overlaps the next piece's GEMMs; every piece must be a
+    multiple of 128 token rows.  Per token the arithmetic is that of chunks = 1 (the ranks' sums may associate
+    differently inside the collective when there are more than two ranks)."""
     if dispatch not in ("replicated", "all_to_all"):
         raise ValueError("dispatch must be 'replicated' or 'all_to_all'")
     if dispatch == "all_to_all":
@@ -338,6 +403,12 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
     if reduce not in ("all_reduce", "reduce_scatter"):
         raise ValueError("reduce must be 'all_reduce' or 'reduce_scatter'")
     partial = (w.last - w.first) < w.experts
+    if chunks > 1 and partial and w.gate_up.format in ("nvfp4", "mxfp4"):
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized():
+            raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")
+        out = _moe_forward_chunked(x, logits, w, k, renormalize, group, reduce, exchange_dtype, chunks)
+        return out if out.dtype == out_dtype else out.to(out_dtype)
     # shares that travel in bf16 are written in bf16 by the combine itself (fp32 sum, one rounding)
     direct = partial and exchange_dtype == torch.bfloat16
     out = moe_partial(x, logits, w, k, renormalize=renormalize, out_dtype=torch.bfloat16 if direct else torch.float32)

@@ -61,6 +61,24 @@ for fmt in ("nvfp4", "bf16"):
     err = float((shard - ref).norm() / ref.norm())
     print(rank, fmt, "moe layer reduce-scatter (bf16 exchange) relF", err, tuple(shard.shape), flush=True)
     ok &= err < 1e-2 and tuple(shard.shape) == (rows, D)
+# the same layer in pipelined pieces (each piece's collective overlaps the next piece's GEMMs): on two ranks the sums are
+# those of the unchunked layer, bit for bit, in both reduce modes; tokens 512 = 2 ranks x 2 pieces x 128 rows
+Tc = 512
+xc = torch.randn(Tc, K, generator=g, device="cuda").bfloat16()
+lc = torch.randn(Tc, E, generator=g, device="cuda")
+for fmt, hgs in (("nvfp4", 0.004), ("mxfp4", None)):
+    wc = MoEWeights.pack(w1, w2, fmt, rank=rank, world=world, hidden_global_scale=hgs)
+    for red, dt in (("reduce_scatter", torch.bfloat16), ("reduce_scatter", None), ("all_reduce", None)):
+        base = moe_forward(xc, lc, wc, k, reduce=red, exchange_dtype=dt)
+        got = moe_forward(xc, lc, wc, k, reduce=red, exchange_dtype=dt, chunks=2)
+        same = bool(torch.equal(got, base))
+        print(rank, fmt, red, dt, "chunked layer identical", same, tuple(got.shape), flush=True)
+        ok &= same
+try:
+    moe_forward(xc[:384], lc[:384], wc, k, reduce="reduce_scatter", chunks=2)
+    ok = False
+except ValueError:
+    pass
 # token all-to-all: every rank owns half of the tokens and half of the experts; bit-identical to one GPU holding all
 for fmt, hgs in (("nvfp4", 0.004), ("nvfp4", None), ("mxfp4", None)):
     whole = moe_forward(xm, lg, MoEWeights.pack(w1, w2, fmt, hidden_global_scale=hgs), k)
