@@ -192,20 +192,21 @@ def _experts_fp4(p: MoEPlan, packed: torch.Tensor, sf: torch.Tensor, gs, w: MoEW
 
 
 def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
-                out_dtype=torch.float32) -> torch.Tensor:
+                out_dtype=torch.float32, act_global_scale=None) -> torch.Tensor:
     """This rank's share of the layer's result, [tokens, D] (fp32, or bf16 = the fp32 sum rounded once, which saves
     a conversion pass when the shares travel in bf16): the sum over the slots routed to its experts.
     NVFP4 / MXFP4 weights take the quantise-once path; with `hidden_global_scale` set (NVFP4) the hidden
     activation is quantised in the epilogue of the gate/up GEMM, otherwise it is written in bf16 and quantised
     by a separate pass (which, when the rank holds only part of the experts, reads the local row count back to
-    the host once)."""
+    the host once).  `act_global_scale` (NVFP4: a number or a one-element tensor) is a calibrated global scale of x;
+    the quantiser then makes ONE pass over x instead of an amax pass and a quantise pass."""
     fmt = w.gate_up.format
     ids, wts = route(logits, k, renormalize)
     p = plan(ids, wts, w.experts)
     offs = _local_offsets(p, w.first, w.last)
     K = x.shape[1]
     if fmt in ("nvfp4", "mxfp4"):
-        packed, sf, gs = quantize_fp4(x, fmt)
+        packed, sf, gs = quantize_fp4(x, fmt, global_scale=act_global_scale if fmt == "nvfp4" else None)
         y = _experts_fp4(p, packed, sf, gs, w, K)
     elif fmt == "fp8":
         # per-tensor scale: taken over the tokens, so that it does not depend on which experts are local;
@@ -271,11 +272,12 @@ def _global_scale_of(amax: torch.Tensor) -> torch.Tensor:
 
 
 def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
-                           out_dtype=torch.float32, group=None) -> torch.Tensor:
+                           out_dtype=torch.float32, group=None, act_global_scale=None) -> torch.Tensor:
     """The layer for a rank that owns the token rows x [tokens_local, K] and the experts w.first .. w.last: returns
     its own tokens' results [tokens_local, D].  NVFP4 / MXFP4 weights.  The NVFP4 global scale of the activations
     is that of ALL ranks' tokens (one all-reduce of a float), so the layer computes exactly what one GPU holding
-    every token would."""
+    every token would; a calibrated `act_global_scale` (number or one-element tensor) replaces it and saves that
+    collective and the amax pass."""
     import torch.distributed as dist
     fmt = w.gate_up.format
     if fmt not in ("nvfp4", "mxfp4"):
@@ -288,9 +290,9 @@ def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights,
     local_experts = w.last - w.first
     ids, wts = route(logits, k, renormalize)
     p = plan(ids, wts, w.experts)
-    gs_in = None
-    if fmt == "nvfp4" and world > 1:
-        amax = x.abs().amax().float().reshape(1)
+    gs_in = act_global_scale if fmt == "nvfp4" else None
+    if fmt == "nvfp4" and world > 1 and gs_in is None:
+        amax = torch.linalg.vector_norm(x, ord=float("inf")).float().reshape(1)       # max |x| in one pass
         dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
         gs_in = _global_scale_of(amax)
     packed, sf, gs = quantize_fp4(x, fmt, global_scale=gs_in)
@@ -318,7 +320,8 @@ def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights,
         # the hidden activation's global scale is that of ALL ranks' rows (every rank joins, also one without rows)
         hgs_in = None
         if fmt == "nvfp4" and world > 1:
-            amax_h = (h.abs().amax().float().reshape(1) if R > 0 else torch.zeros(1, dtype=torch.float32, device=dev))
+            amax_h = (torch.linalg.vector_norm(h, ord=float("inf")).float().reshape(1) if R > 0
+                      else torch.zeros(1, dtype=torch.float32, device=dev))
             dist.all_reduce(amax_h, op=dist.ReduceOp.MAX, group=group)
             hgs_in = _global_scale_of(amax_h)
         if R > 0:
@@ -334,7 +337,7 @@ def moe_forward_all_to_all(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights,
 
 
 def _moe_forward_chunked(x, logits, w: MoEWeights, k: int, renormalize: bool, group, reduce: str, exchange_dtype,
-                         chunks: int) -> torch.Tensor:
+                         chunks: int, act_global_scale=None) -> torch.Tensor:
     """Expert-parallel layer (replicated routing, NVFP4 / MXFP4) in `chunks` pipelined pieces: routing and the activation
     quantiser run once over all tokens (so the NVFP4 global scale is the whole tensor's, as without chunks), then every
     piece is dispatched, multiplied and combined on the compute stream while the previous piece's partial results
@@ -354,7 +357,7 @@ def _moe_forward_chunked(x, logits, w: MoEWeights, k: int, renormalize: bool, gr
         raise ValueError(f"chunks={chunks}: every piece must be a multiple of 128 token rows "
                          f"(tokens {T}, ranks {world if scatter else 1})")
     ids, wts = route(logits, k, renormalize)
-    packed, sf, gs = quantize_fp4(x, fmt)
+    packed, sf, gs = quantize_fp4(x, fmt, global_scale=act_global_scale if fmt == "nvfp4" else None)
     nblk = K // 16 if fmt == "nvfp4" else K // 32
     tile_bytes = ((nblk + 3) // 4) * 512                              # one 128-row scale tile row of the plain layout
     outer = world if scatter else 1
@@ -384,7 +387,7 @@ def _moe_forward_chunked(x, logits, w: MoEWeights, k: int, renormalize: bool, gr
 
 def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
                 out_dtype=torch.float32, group=None, reduce: str = "all_reduce", exchange_dtype=None,
-                dispatch: str = "replicated", chunks: int = 1) -> torch.Tensor:
+                dispatch: str = "replicated", chunks: int = 1, act_global_scale=None) -> torch.Tensor:
     """One MoE feed-forward layer: x [tokens, K], router logits [tokens, experts] -> [tokens, D].
     dispatch "all_to_all": x / logits are this rank's OWN token rows and the result is theirs
     (`moe_forward_all_to_all`); the remaining arguments below apply to "replicated".
@@ -395,11 +398,14 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
     partial results before they travel; default fp32.  `chunks` > 1 (NVFP4 / MXFP4 weights, expert-parallel) runs the
     layer in that many pieces so that each piece's collective overlaps the next piece's GEMMs; every piece must be a
     multiple of 128 token rows.  Per token the arithmetic is that of chunks = 1 (the ranks' sums may associate
-    differently inside the collective when there are more than two ranks)."""
+    differently inside the collective when there are more than two ranks).  `act_global_scale` (NVFP4 weights): a
+    calibrated global scale of x (number or one-element tensor) instead of amax / 2688 - one quantiser pass, no
+    collective for it in the all-to-all form."""
     if dispatch not in ("replicated", "all_to_all"):
         raise ValueError("dispatch must be 'replicated' or 'all_to_all'")
     if dispatch == "all_to_all":
-        return moe_forward_all_to_all(x, logits, w, k, renormalize=renormalize, out_dtype=out_dtype, group=group)
+        return moe_forward_all_to_all(x, logits, w, k, renormalize=renormalize, out_dtype=out_dtype, group=group,
+                                      act_global_scale=act_global_scale)
     if reduce not in ("all_reduce", "reduce_scatter"):
         raise ValueError("reduce must be 'all_reduce' or 'reduce_scatter'")
     partial = (w.last - w.first) < w.experts
@@ -407,11 +413,12 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized():
             raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")
-        out = _moe_forward_chunked(x, logits, w, k, renormalize, group, reduce, exchange_dtype, chunks)
+        out = _moe_forward_chunked(x, logits, w, k, renormalize, group, reduce, exchange_dtype, chunks, act_global_scale)
         return out if out.dtype == out_dtype else out.to(out_dtype)
     # shares that travel in bf16 are written in bf16 by the combine itself (fp32 sum, one rounding)
     direct = partial and exchange_dtype == torch.bfloat16
-    out = moe_partial(x, logits, w, k, renormalize=renormalize, out_dtype=torch.bfloat16 if direct else torch.float32)
+    out = moe_partial(x, logits, w, k, renormalize=renormalize, out_dtype=torch.bfloat16 if direct else torch.float32,
+                      act_global_scale=act_global_scale)
     if partial:
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized():

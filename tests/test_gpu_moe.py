@@ -181,6 +181,25 @@ def test_all_to_all_path_on_one_rank_equals_the_replicated_layer(cuda_device, fm
     assert torch.equal(got, base)
 
 
+def test_calibrated_activation_scale_in_the_layer(cuda_device):
+    """act_global_scale replaces amax / 2688 of the tokens: given the very scale the dynamic path derives, the layer's
+    bits do not change (both dispatch forms); given another one, the result moves a little and both forms still agree."""
+    rng = np.random.default_rng(62)
+    T, E, k, K, H, Dm = 200, 5, 2, 256, 128, 192
+    x, logits, w1, w2 = _layer_inputs(rng, T, E, K, H, Dm, cuda_device)
+    wts = D.MoEWeights.pack(w1, w2, "nvfp4", hidden_global_scale=0.004)
+    base = D.moe_forward(x, logits, wts, k)
+    _, _, gs = D.quantize_fp4(x, "nvfp4")
+    for given in (gs, float(gs.item())):
+        assert torch.equal(D.moe_forward(x, logits, wts, k, act_global_scale=given), base)
+        assert torch.equal(D.moe_forward(x, logits, wts, k, act_global_scale=given, dispatch="all_to_all"), base)
+    other = D.moe_forward(x, logits, wts, k, act_global_scale=float(gs.item()) * 1.3)
+    assert torch.equal(D.moe_forward(x, logits, wts, k, act_global_scale=float(gs.item()) * 1.3, dispatch="all_to_all"), other)
+    rel = float((other - base).norm() / base.norm())
+    assert 0 < rel < 0.05, rel
+    _lib.check_status()
+
+
 def test_wire_records_round_trip(cuda_device):
     """pack -> unpack of the wire records reproduces dispatch_fp4's expert-sorted rows and scale tiles bit for bit."""
     rng = np.random.default_rng(61)

@@ -89,6 +89,14 @@ for fmt, hgs in (("nvfp4", 0.004), ("nvfp4", None), ("mxfp4", None)):
     same = bool(torch.equal(got, whole[mine]))
     print(rank, fmt, hgs, "moe layer token all-to-all identical", same, tuple(got.shape), flush=True)
     ok &= same
+# a calibrated activation scale: no amax collective, still the bits of one GPU holding every token
+whole = moe_forward(xm, lg, MoEWeights.pack(w1, w2, "nvfp4", hidden_global_scale=0.004), k, act_global_scale=0.002)
+got = moe_forward(xm[mine].contiguous(), lg[mine].contiguous(),
+                  MoEWeights.pack(w1, w2, "nvfp4", rank=rank, world=world, hidden_global_scale=0.004), k, dispatch="all_to_all",
+                  act_global_scale=0.002)
+same = bool(torch.equal(got, whole[mine]))
+print(rank, "all-to-all with a calibrated activation scale identical", same, flush=True)
+ok &= same
 # a rank that receives nothing: every token prefers the experts of rank 0
 lg0 = lg.clone(); lg0[:, E // 2:] = -1e9
 whole = moe_forward(xm, lg0, MoEWeights.pack(w1, w2, "nvfp4", hidden_global_scale=None), k)
