@@ -686,6 +686,69 @@ quant_nvfp4_token_kernel(const T* __restrict__ x, long long M, int K, float* __r
     }
 }
 
+// The same per-token quantiser with ONE WARP per row, for bf16 rows of up to 4096 elements (R = chunks per lane, row
+// length up to R * 512): the row maximum needs only shuffles - no shared memory, no block barrier - so the warps of a CTA
+// run independently and the loads of many rows are in flight per SM.  The CTA-per-row form above spends most of a short
+// row's time in its two barriers (131072 rows of 4096: 0.49 ms, 2.8 TB/s).
+template <int R>
+__global__ void __launch_bounds__(256)
+quant_nvfp4_token_warp_kernel(const __nv_bfloat16* __restrict__ x, long long M, int K, float* __restrict__ gs_out,
+                              uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const int* __restrict__ group_offsets,
+                              int num_groups, bool wide) {
+    griddep_launch_dependents();
+    __shared__ int s_offs[kMaxGroups + 1];
+    __shared__ int s_tile0[kMaxGroups + 1];
+    const int cpr = K / 16;
+    SfIndexer sfi;
+    sf_indexer_init(sfi, s_offs, s_tile0, group_offsets, num_groups, static_cast<int>(M), cpr, false);
+    const bool packed = (cpr % 4) == 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row_blocks = (M + 7) / 8;
+    for (long long rb = blockIdx.x; rb < row_blocks; rb += gridDim.x) {
+        const long long row = rb * 8 + warp;               // ascending per warp: the indexer's cursor relies on it
+        const bool row_ok = row < M;
+        Chunk16<__nv_bfloat16> ch[R];
+        float bm[R];
+        float m = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int kc = lane + 32 * r;
+            if (row_ok && kc < cpr) ch[r].load(x + (static_cast<size_t>(row) * cpr + kc) * 16, wide);
+            else ch[r].zero();
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            bm[r] = ch[r].amax();
+            m = fmaxf(m, bm[r]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        const float gs = m == 0.f ? 1.0f : __fdiv_rn(m, 2688.0f);
+        if (lane == 0 && row_ok) gs_out[row] = gs;
+        Nvfp4Scaler scaler;
+        scaler.init(gs);
+        const long long base = row_ok ? sfi.row_base(static_cast<unsigned>(row)) : -1;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int kc = lane + 32 * r;
+            const bool valid = row_ok && kc < cpr;
+            float inv;
+            const uint32_t sfb = scaler(bm[r], inv);
+            if (valid) *reinterpret_cast<uint2*>(q + (static_cast<size_t>(row) * cpr + kc) * 8) = ch[r].quant_e2m1(inv);
+            uint8_t* dst = sf + base + static_cast<size_t>(kc >> 2) * 512 + (kc & 3);
+            if (packed) {
+                uint32_t word = sfb;
+                word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 1) << 8;
+                word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 2) << 16;
+                word |= __shfl_down_sync(0xFFFFFFFFu, sfb, 3) << 24;
+                if (valid && base >= 0 && (kc & 3) == 0) *reinterpret_cast<uint32_t*>(dst) = word;
+            } else if (valid && base >= 0) {
+                *dst = static_cast<uint8_t>(sfb);
+            }
+        }
+    }
+}
+
 // Small tensors (decode: a handful of activation rows): tensor amax, global scale and the NVFP4
 // quantisation in ONE launch of a single CTA, instead of memset + amax + scale + quantise.
 template <typename T>
@@ -977,6 +1040,16 @@ static cudaError_t quant_token_typed(const T* x, long long rows, long long cols,
     // One row per CTA and pass (ROWS = 1).  Taking several rows at a time to keep more loads in flight was measured
     // and lost (8192 x 8192: 59 -> 68 us, 131072 x 4096: 563 -> 627 us): the kernel is bound by instruction issue, and
     // the extra registers (128 instead of about 48 per thread) halve the warps that can hide each other's latencies.
+    if (sizeof(T) == 2 && !dsl_is_half<T>::value && cpr <= 256) {     // bf16 rows of up to 4096 elements: a warp per row
+        const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+        const long long row_blocks = (rows + 7) / 8;
+        const unsigned wgrid = static_cast<unsigned>(row_blocks < 148 * 4 ? row_blocks : 148 * 4);
+        if (cpr <= 32) quant_nvfp4_token_warp_kernel<1><<<wgrid, 256, 0, st>>>(xb, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+        else if (cpr <= 64) quant_nvfp4_token_warp_kernel<2><<<wgrid, 256, 0, st>>>(xb, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+        else if (cpr <= 128) quant_nvfp4_token_warp_kernel<4><<<wgrid, 256, 0, st>>>(xb, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+        else quant_nvfp4_token_warp_kernel<8><<<wgrid, 256, 0, st>>>(xb, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
+        return cudaGetLastError();
+    }
     const unsigned grid = static_cast<unsigned>(rows < 148 * 8 ? rows : 148 * 8);
     if (cpr <= 256) quant_nvfp4_token_kernel<T, 1, 1><<<grid, 256, 0, st>>>(x, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);
     else if (cpr <= 512) quant_nvfp4_token_kernel<T, 2, 1><<<grid, 256, 0, st>>>(x, rows, k, gs_out, q, sf, group_offsets, num_groups, wide);

@@ -97,10 +97,11 @@ def test_input_that_is_only_16_byte_aligned(cuda_device, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(1, 32), (7, 96), (129, 1056), (300, 4096), (40, 8192), (9, 28672)])
+@pytest.mark.parametrize("shape", [(1, 32), (7, 96), (50, 768), (129, 1056), (300, 4096), (40, 8192), (9, 28672)])
 def test_nvfp4_per_token_scales(cuda_device, shape, dtype):
     """global_scale="per_token": one pass; bytes, scale tiles and the per-row global scales equal the oracle's (every
-    register-chunk count of the kernel: rows of 32 ... 28672 elements; an all-zero row gets scale 1 and zero bytes)."""
+    register-chunk count of both kernels - a warp per row up to 4096 bf16 elements, a CTA per row beyond and for the
+    other types: rows of 32 ... 28672 elements; an all-zero row gets scale 1 and zero bytes)."""
     from dsl_tool_b200 import quantize_fp4
     xc, xo = _inputs(shape, dtype, 21)
     q, sf, gs = quantize_fp4(xc, "nvfp4", global_scale="per_token")
@@ -120,6 +121,13 @@ def test_nvfp4_per_token_ragged_groups_and_limits(cuda_device):
     assert np.array_equal(gs.cpu().numpy(), pgs) and np.array_equal(q.cpu().numpy(), pq)
     want = O.swizzle_sf_grouped(psf, offs)
     assert np.array_equal(sf.cpu().numpy()[: want.size], want)
+    for dtype, K in ((torch.bfloat16, 2048), (torch.float32, 2048), (torch.bfloat16, 8192)):    # warp per row / CTA per row
+        xc, xo = _inputs((300, K), dtype, 23)
+        q, sf, gs = quantize_fp4(xc, "nvfp4", global_scale="per_token", group_offsets=torch.from_numpy(offs).cuda())
+        pq, psf, pgs = O.quant_nvfp4(xo, "per_token")
+        assert np.array_equal(gs.cpu().numpy(), pgs) and np.array_equal(q.cpu().numpy(), pq)
+        want = O.swizzle_sf_grouped(psf, offs)
+        assert np.array_equal(sf.cpu().numpy()[: want.size], want)
     with pytest.raises(ValueError, match="at most"):
         quantize_fp4(torch.zeros(2, 32768 + 32, device="cuda"), "nvfp4", global_scale="per_token")
     with pytest.raises(ValueError, match="per_token"):
