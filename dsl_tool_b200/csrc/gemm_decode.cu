@@ -638,6 +638,8 @@ static int launch_decode_one(const void* A, const void* B, const GemmArgs& args,
     }
     // Programmatic stream serialisation: the grid may be set up (and, for a static weight, start its
     // weight stream) while the preceding kernel of the stream drains; griddep_wait() guards the rest.
+    // DSLGEMM_PDL=0 launches it the plain way (for measurements).
+    static const bool pdl = [] { const char* e = getenv("DSLGEMM_PDL"); return !(e != nullptr && e[0] == '0'); }();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(plan.ctas);
     cfg.blockDim = dim3(192);
@@ -645,7 +647,7 @@ static int launch_decode_one(const void* A, const void* B, const GemmArgs& args,
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
     cfg.numAttrs = 1;
     if (plan.cluster_runs > 1) {
         attr[1].id = cudaLaunchAttributeClusterDimension;
