@@ -88,6 +88,10 @@ WORKLOADS = {
     # (measured slower than the unchunked layer on 2 and 4 GPUs, so it is not part of the sweep; --workload runs it)
     "moe_layer_nvfp4_overlap": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
                                     hidden_gs=0.01, chunks=2),
+    # the replicated-routing layer whose shares are summed by the library's own kernel over peer memory (symmetric
+    # memory, plain NVLink loads) instead of NCCL's reduce-scatter
+    "moe_layer_nvfp4_pull": dict(kind="nvfp4", layer=True, tokens=16384, topk=8, experts=64, K=4096, H=1536, D=4096, wstd=0.02,
+                                 hidden_gs=0.01, pull=True),
     "bf16_8192": dict(kind="bf16", M=8192, K=8192, N=8192, wstd=0.02, outliers=False),
 }
 DEFAULT_WORKLOAD = "fp8_groupwise_llama8b_mlp"
@@ -97,7 +101,7 @@ SWEEP_1GPU = ["fp8_per_tensor_1024", "fp8_groupwise_8192", "nvfp4_8192", "nvfp4_
               "moe_fp8_groupwise", "moe_fp8_groupwise_tokens", "moe_layer_nvfp4"]
 # ... and the sharded ones when the problem is split over several GPUs
 SWEEP_SHARDED = ["mxfp4_llama70b_up", "mxfp4_llama70b_up_gather", "mxfp4_llama70b_down", "moe_nvfp4", "moe_fp8_groupwise",
-                 "moe_layer_nvfp4", "moe_layer_nvfp4_a2a"]
+                 "moe_layer_nvfp4", "moe_layer_nvfp4_pull", "moe_layer_nvfp4_a2a"]
 DTYPE_NAME = {"fp8": "fp8_e4m3", "fp8_block128": "fp8_e4m3", "nvfp4": "fp4_e2m1", "mxfp4": "fp4_e2m1", "bf16": "bf16"}
 # dram__bytes_read.sum + dram__bytes_write.sum of the GEMM kernel per launch, from ncu captures of the
 # full-size workloads: bytes.  None where no capture exists.
@@ -264,6 +268,7 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
     T, E, k, K, H, D = cfg["tokens"], cfg["experts"], cfg["topk"], cfg["K"], cfg["H"], cfg["D"]
     a2a = bool(cfg.get("a2a")) and strong and world > 1
     chunks = int(cfg.get("chunks", 1)) if strong and world > 1 else 1
+    red = "pull" if cfg.get("pull") and strong and world > 1 else "reduce_scatter"
     mine = slice(rank * (T // world), (rank + 1) * (T // world)) if a2a else slice(0, T)
     acts, logits, wts = [], [], []
     for s in range(sets):
@@ -283,7 +288,7 @@ def build_layer_workload(cfg, rank, world, device, sets, strong, g):
                                dispatch="all_to_all")
         # expert-parallel ranks exchange bf16 partial results and keep their own token rows (reduce-scatter)
         return moe_forward(acts[i % sets] if a is None else a, logits[i % sets], wts[i % sets], k, out_dtype=torch.bfloat16,
-                           reduce="reduce_scatter", exchange_dtype=torch.bfloat16, chunks=chunks)
+                           reduce=red, exchange_dtype=torch.bfloat16, chunks=chunks)
 
     flops = 2.0 * T * k * (2 * H * K + D * H) / (world if strong else 1)
     return dict(step=step, acts=acts, wts=wts, offs=None, M=T * k, K=K, N=2 * H, kind=cfg["kind"], flops=flops, moe=True,

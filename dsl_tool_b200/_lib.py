@@ -106,6 +106,7 @@ _SIGNATURES = {
     "dsl_moe_dispatch_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _ll, _i, _i, _vp, _vp]),
     "dsl_moe_combine": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "dsl_moe_wire_bytes": (ctypes.c_size_t, [_i, _i]),
+    "dsl_moe_reduce_pull": (_i, [ctypes.POINTER(ctypes.c_void_p), _i, _ll, _ll, _i, _i, _vp, _i, _vp]),
     "dsl_moe_pack_wire_fp4": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "dsl_moe_unpack_wire_fp4": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "dsl_gemm_bf16": (_i, [_vp, _vp, _vp, _ll, _ll, _i, _i, _vp, _i, ctypes.POINTER(Epilogue), _vp, _vp]),

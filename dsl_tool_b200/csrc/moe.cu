@@ -418,6 +418,98 @@ extern "C" int dsl_moe_combine(const void* y, int y_dtype, const int* ids, const
     return static_cast<int>(cudaGetLastError());
 }
 
+// ---- sum of the ranks' partial results over peer memory -----------------------------------------
+// Every rank holds a partial result [total rows, D] in memory that its peers can address (mapped into this process by
+// the caller, e.g. symmetric memory).  Rank r wants rows [row0, row0 + rows) of the sum: each thread takes one 16-byte
+// vector, loads it from every rank's buffer (plain loads: the local one from HBM, the others over NVLink - no TMA, no
+// multicast, nothing is written to a peer), adds in rank order in fp32 and stores the result locally.  The order is
+// fixed, so the result does not depend on timing.  The caller orders the kernel after every rank's partial result is
+// complete (a collective on the stream) and keeps a buffer untouched until every rank has read it.
+struct PeerPtrs {
+    const void* p[DSL_MAX_PEERS];
+};
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+moe_reduce_pull_kernel(PeerPtrs ptrs, int world, size_t first_vec, size_t nvec, TO* __restrict__ out) {
+    constexpr int VEC = 16 / sizeof(TI);
+    for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        uint4 part[DSL_MAX_PEERS];
+#pragma unroll
+        for (int s = 0; s < DSL_MAX_PEERS; ++s)
+            if (s < world) part[s] = __ldcg(reinterpret_cast<const uint4*>(ptrs.p[s]) + first_vec + v);   // all in flight together
+        float acc[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
+#pragma unroll
+        for (int s = 0; s < DSL_MAX_PEERS; ++s) {
+            if (s >= world) break;
+            if (sizeof(TI) == 4) {
+                const float* f = reinterpret_cast<const float*>(&part[s]);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+            } else {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[s]);
+#pragma unroll
+                for (int j = 0; j < VEC / 2; ++j) {
+                    const float2 f = __bfloat1622float2(h[j]);
+                    acc[2 * j] = __fadd_rn(acc[2 * j], f.x);
+                    acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], f.y);
+                }
+            }
+        }
+        if (sizeof(TO) == 4) {
+            float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + v * VEC);
+#pragma unroll
+            for (int j = 0; j < VEC / 4; ++j) o[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+        } else if (VEC == 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + v * VEC) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+            uint32_t w[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + v * VEC) = make_uint2(w[0], w[1]);
+        }
+    }
+}
+
+extern "C" int dsl_moe_reduce_pull(const void* const* part_ptrs, int world, long long row0, long long rows, int d_model,
+                                   int in_dtype, void* out, int out_dtype, void* stream) {
+    if (part_ptrs == nullptr || out == nullptr) return DSL_ERR_NULL;
+    if (world < 1 || world > DSL_MAX_PEERS) return DSL_ERR_TOO_LARGE;
+    if ((in_dtype != DSL_F32 && in_dtype != DSL_BF16) || (out_dtype != DSL_F32 && out_dtype != DSL_BF16)) return DSL_ERR_ENUM;
+    if (row0 < 0 || rows < 0 || d_model < 1) return DSL_ERR_SHAPE;
+    const int vec = in_dtype == DSL_F32 ? 4 : 8;
+    if (d_model % vec != 0) return DSL_ERR_SHAPE;              // rows are whole 16-byte vectors
+    PeerPtrs ptrs;
+    for (int s = 0; s < DSL_MAX_PEERS; ++s) {
+        ptrs.p[s] = s < world ? part_ptrs[s] : nullptr;
+        if (s < world && ptrs.p[s] == nullptr) return DSL_ERR_NULL;
+        if (s < world && (reinterpret_cast<uintptr_t>(ptrs.p[s]) & 15u) != 0) return DSL_ERR_ALIGN;
+    }
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return DSL_ERR_ALIGN;
+    if (rows == 0) return 0;
+    const size_t per_row = static_cast<size_t>(d_model) / vec;
+    const size_t nvec = static_cast<size_t>(rows) * per_row;
+    const size_t first_vec = static_cast<size_t>(row0) * per_row;
+    const size_t want = (nvec + 255) / 256;
+    const unsigned grid = static_cast<unsigned>(want < 148u * 16u ? want : 148u * 16u);
+    cudaStream_t st = st_of(stream);
+    if (in_dtype == DSL_F32 && out_dtype == DSL_F32) moe_reduce_pull_kernel<float, float><<<grid, 256, 0, st>>>(ptrs, world, first_vec, nvec, static_cast<float*>(out));
+    else if (in_dtype == DSL_F32) moe_reduce_pull_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>(ptrs, world, first_vec, nvec, static_cast<__nv_bfloat16*>(out));
+    else if (out_dtype == DSL_F32) moe_reduce_pull_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>(ptrs, world, first_vec, nvec, static_cast<float*>(out));
+    else moe_reduce_pull_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(ptrs, world, first_vec, nvec, static_cast<__nv_bfloat16*>(out));
+    return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" size_t dsl_moe_wire_bytes(int K, int format) {
     if (K <= 0 || K % 32 != 0 || (format != DSL_FP4_NV && format != DSL_FP4_MX)) return 0;
     const int nblk = format == DSL_FP4_NV ? K / 16 : K / 32;

@@ -192,7 +192,7 @@ def _experts_fp4(p: MoEPlan, packed: torch.Tensor, sf: torch.Tensor, gs, w: MoEW
 
 
 def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *, renormalize: bool = True,
-                out_dtype=torch.float32, act_global_scale=None) -> torch.Tensor:
+                out_dtype=torch.float32, act_global_scale=None, out=None) -> torch.Tensor:
     """This rank's share of the layer's result, [tokens, D] (fp32, or bf16 = the fp32 sum rounded once, which saves
     a conversion pass when the shares travel in bf16): the sum over the slots routed to its experts.
     NVFP4 / MXFP4 weights take the quantise-once path; with `hidden_global_scale` set (NVFP4) the hidden
@@ -231,7 +231,7 @@ def moe_partial(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
         rows = dispatch_rows(p, x.to(torch.bfloat16), w.first, w.last)
         h = linear(rows, w.gate_up, expert_offsets=offs, activation="swiglu", out_dtype=torch.bfloat16)
         y = linear(h, w.down, expert_offsets=offs, out_dtype=torch.bfloat16)
-    return combine(p, y, w.first, w.last, out_dtype=out_dtype)
+    return combine(p, y, w.first, w.last, out_dtype=out_dtype, out=out)
 
 
 def pack_wire(p: MoEPlan, packed: torch.Tensor, sf: torch.Tensor, K: int, format: str) -> torch.Tensor:
@@ -394,7 +394,9 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
     When `w` covers only part of the experts the per-rank partial results are summed over `group` (default: the
     default process group of torch.distributed): reduce "all_reduce" leaves the whole result on every rank,
     "reduce_scatter" leaves rank r with token rows [r * tokens / world, (r + 1) * tokens / world) - half the
-    traffic, and what a sequence-sharded consumer wants.  `exchange_dtype` (e.g. torch.bfloat16) rounds the
+    traffic, and what a sequence-sharded consumer wants; "pull" gives the same rows without a data-moving collective:
+    the shares sit in symmetric memory and `dsl_moe_reduce_pull` reads the rank's rows of every share over NVLink
+    and adds them in rank order (`sharding.PeerReducer`; one small all-reduce per layer serves as the barrier).  `exchange_dtype` (e.g. torch.bfloat16) rounds the
     partial results before they travel; default fp32.  `chunks` > 1 (NVFP4 / MXFP4 weights, expert-parallel) runs the
     layer in that many pieces so that each piece's collective overlaps the next piece's GEMMs; every piece must be a
     multiple of 128 token rows.  Per token the arithmetic is that of chunks = 1 (the ranks' sums may associate
@@ -406,15 +408,27 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, w: MoEWeights, k: int, *,
     if dispatch == "all_to_all":
         return moe_forward_all_to_all(x, logits, w, k, renormalize=renormalize, out_dtype=out_dtype, group=group,
                                       act_global_scale=act_global_scale)
-    if reduce not in ("all_reduce", "reduce_scatter"):
-        raise ValueError("reduce must be 'all_reduce' or 'reduce_scatter'")
+    if reduce not in ("all_reduce", "reduce_scatter", "pull"):
+        raise ValueError("reduce must be 'all_reduce', 'reduce_scatter' or 'pull'")
     partial = (w.last - w.first) < w.experts
+    if chunks > 1 and reduce == "pull":
+        raise ValueError("chunks > 1 goes with reduce='all_reduce' or 'reduce_scatter'")
     if chunks > 1 and partial and w.gate_up.format in ("nvfp4", "mxfp4"):
         import torch.distributed as dist
         if not dist.is_available() or not dist.is_initialized():
             raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")
         out = _moe_forward_chunked(x, logits, w, k, renormalize, group, reduce, exchange_dtype, chunks, act_global_scale)
         return out if out.dtype == out_dtype else out.to(out_dtype)
+    if partial and reduce == "pull":
+        # every rank writes its share into symmetric memory and reads its own token rows of all shares over NVLink
+        import torch.distributed as dist
+        from .sharding import peer_reducer
+        if not dist.is_available() or not dist.is_initialized():
+            raise RuntimeError("these weights cover only part of the experts: initialise torch.distributed")
+        dt = exchange_dtype if exchange_dtype is not None else torch.float32
+        red = peer_reducer(x.shape[0], w.down.n, dt, x.device, group)
+        moe_partial(x, logits, w, k, renormalize=renormalize, act_global_scale=act_global_scale, out=red.buffer())
+        return red.reduce(out_dtype)
     # shares that travel in bf16 are written in bf16 by the combine itself (fp32 sum, one rounding)
     direct = partial and exchange_dtype == torch.bfloat16
     out = moe_partial(x, logits, w, k, renormalize=renormalize, out_dtype=torch.bfloat16 if direct else torch.float32,

@@ -217,3 +217,80 @@ def shard_weight_columns(w_nk: torch.Tensor, rank: int, world: int) -> torch.Ten
 def shard_weight_experts(w_gnk: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     f, l = expert_ranges(w_gnk.shape[0], world)[rank]
     return w_gnk[f:l]
+
+
+# ---- sum of the ranks' partial results over peer memory (own kernel, plain loads over NVLink) ----
+
+class PeerReducer:
+    """The ranks' partial results [rows, cols] summed by reading the peers' buffers directly, every rank keeping its
+    rows [rank * rows / world, (rank + 1) * rows / world): the reduce-scatter of an expert-parallel layer without a
+    collective library moving the data.
+
+    Each rank writes its partial result into `buffer()` (symmetric memory: the same allocation on every rank, mapped into
+    every peer).  `reduce()` first runs a one-element NCCL all-reduce on the stream - a barrier that tells every rank that
+    all buffers are complete, and that honours the process group's time limit if a rank is missing - and then launches
+    `dsl_moe_reduce_pull`, which loads the rank's own rows from all `world` buffers and adds them in rank order in fp32.
+    Two buffers alternate, so a rank can start writing the next step's partial result while its peers still read this
+    step's; by the time it comes back to a buffer, every rank has passed another barrier and is done reading it.
+    Nothing is written to a peer and no TMA or multicast instruction touches peer memory; the multicast binding of the
+    symmetric allocation is switched off (TORCH_SYMM_MEM_DISABLE_MULTICAST), the loads are plain ones."""
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, device, group=None):
+        import ctypes
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError("partial results travel as float32 or bfloat16")
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        if rows % self.world:
+            raise ValueError(f"the row count ({rows}) must be a multiple of the group size ({self.world})")
+        if (cols * torch.empty((), dtype=dtype).element_size()) % 16:
+            raise ValueError("a row must be a whole number of 16-byte vectors")
+        self.rows, self.cols, self.dtype, self.device = rows, cols, dtype, torch.device(device)
+        self._bufs, self._handles, self._ptrs = [], [], []
+        for _ in range(2):
+            t = symm_mem.empty((rows, cols), dtype=dtype, device=self.device)
+            h = symm_mem.rendezvous(t, self.group)
+            ptrs = [int(p) for p in h.buffer_ptrs]
+            if len(ptrs) != self.world or any(p == 0 or p % 16 for p in ptrs) or ptrs[self.rank] != t.data_ptr():
+                raise RuntimeError("symmetric memory did not map every rank's buffer")
+            self._bufs.append(t)
+            self._handles.append(h)
+            self._ptrs.append((ctypes.c_void_p * self.world)(*ptrs))
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._step = 0
+
+    def buffer(self) -> torch.Tensor:
+        """Where this rank writes its partial result of the current step ([rows, cols], local memory)."""
+        return self._bufs[self._step & 1]
+
+    def reduce(self, out_dtype=None) -> torch.Tensor:
+        """This rank's rows of the sum over the ranks' `buffer()`s, [rows / world, cols]; advances to the other buffer."""
+        from . import _lib
+        out_dtype = out_dtype or self.dtype
+        dist.all_reduce(self._flag, group=self.group)          # every rank's buffer is complete from here on
+        per = self.rows // self.world
+        out = torch.empty((per, self.cols), dtype=out_dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().dsl_moe_reduce_pull(self._ptrs[self._step & 1], self.world, self.rank * per, per, self.cols,
+                                                _lib.dtype_code(self.dtype), out.data_ptr(), _lib.dtype_code(out_dtype),
+                                                _lib.stream_ptr())
+        _lib.check(rc, "dsl_moe_reduce_pull")
+        self._step += 1
+        return out
+
+
+_PEER_REDUCERS = {}
+
+
+def peer_reducer(rows: int, cols: int, dtype: torch.dtype, device, group=None) -> PeerReducer:
+    """The PeerReducer of this shape on this group (created, i.e. allocated and exchanged among the ranks, on first use:
+    every rank must ask for it at the same point)."""
+    g = group if group is not None else dist.group.WORLD
+    key = (id(g), rows, cols, dtype, torch.device(device))
+    red = _PEER_REDUCERS.get(key)
+    if red is None:
+        red = _PEER_REDUCERS[key] = PeerReducer(rows, cols, dtype, device, g)
+    return red

@@ -279,6 +279,20 @@ int dsl_moe_combine(const void* y, int y_dtype, const int* ids, const int* dest,
                     int tokens, int k, int d_model, int first_expert, int last_expert, void* out, int out_dtype,
                     void* stream);
 size_t dsl_moe_wire_bytes(int K, int format);
+/*
+ * Sum of the ranks' partial results over peer memory (expert-parallel layer whose ranks keep their own token rows; no
+ * counterpart in the reference).  part_ptrs: HOST array of `world` device pointers, entry s = rank s's partial result
+ * [total rows, d_model] (float32 or bfloat16, contiguous, 16-byte aligned), each addressable from this device - this
+ * rank's own buffer and its peers' buffers mapped by the caller (CUDA IPC / symmetric memory).  Writes
+ * out[r, :] = sum over s = 0 .. world-1, in that order, in fp32, of part_s[row0 + r, :] for r < rows.  The peers'
+ * buffers are only read, with plain loads (no TMA, no multicast).  The caller orders the call after every rank has
+ * finished writing its buffer (a collective or barrier on the stream) and does not overwrite a buffer before every rank
+ * has read it (two alternating buffers and one barrier per step suffice).  d_model must be a whole number of 16-byte
+ * vectors; at most DSL_MAX_PEERS ranks.
+ */
+#define DSL_MAX_PEERS 16
+int dsl_moe_reduce_pull(const void* const* part_ptrs, int world, long long row0, long long rows, int d_model, int in_dtype,
+                        void* out, int out_dtype, void* stream);
 int dsl_moe_pack_wire_fp4(const uint8_t* q_in, const uint8_t* sf_in, const int* dest, int tokens, int k, int K, int format,
                           uint8_t* wire_out, void* stream);
 int dsl_moe_unpack_wire_fp4(const uint8_t* wire_in, const int* ids, const int* dest, const int* offsets, const int* tile0,

@@ -79,6 +79,30 @@ try:
     ok = False
 except ValueError:
     pass
+# the same reduce-scatter with the library's own kernel reading the peers' shares over NVLink (symmetric memory).  Shares
+# that travel in fp32: on two ranks a + b is one addition whichever way, so the bits are NCCL's.  Shares in bf16: the kernel
+# returns the fp32 sum of the two bf16 shares where NCCL rounds it to bf16, so the two agree to bf16 precision and the
+# kernel's rounds agree with each other exactly.  Three rounds, so that both buffers are used again.
+for fmt, hgs in (("nvfp4", 0.004), ("bf16", None)):
+    wp = MoEWeights.pack(w1, w2, fmt, rank=rank, world=world, hidden_global_scale=hgs)
+    for dt in (torch.bfloat16, None):
+        base = moe_forward(xc, lc, wp, k, reduce="reduce_scatter", exchange_dtype=dt)
+        first = None
+        for rnd in range(3):
+            got = moe_forward(xc, lc, wp, k, reduce="pull", exchange_dtype=dt)
+            first = got if first is None else first
+            if dt is None:
+                same = bool(torch.equal(got, base))
+            else:
+                same = bool(torch.equal(got, first)) and bool(torch.equal(got.bfloat16(), base.bfloat16()))
+            print(rank, fmt, dt, "pull round", rnd, "agrees with reduce-scatter", same, tuple(got.shape), flush=True)
+            ok &= same
+    # a different input in between: a stale buffer would show
+    other = moe_forward((xc * 0.5).contiguous(), lc, wp, k, reduce="reduce_scatter")
+    got = moe_forward((xc * 0.5).contiguous(), lc, wp, k, reduce="pull")
+    same = bool(torch.equal(got, other))
+    print(rank, fmt, "pull after a different input identical", same, flush=True)
+    ok &= same
 # token all-to-all: every rank owns half of the tokens and half of the experts; bit-identical to one GPU holding all
 for fmt, hgs in (("nvfp4", 0.004), ("nvfp4", None), ("mxfp4", None)):
     whole = moe_forward(xm, lg, MoEWeights.pack(w1, w2, fmt, hidden_global_scale=hgs), k)
