@@ -122,5 +122,11 @@ def test_new_argument_validation_without_gpu(cdll):
     assert cdll.dsl_moe_dispatch_fp4(p, p, p, p, p, p, 4, 2, 48, 0, 0, 4, p, p, None) == -2            # K % 32
     assert cdll.dsl_moe_dispatch_rows(p, p, p, p, 4, 2, 24, 0, 4, p, None) == -2                       # row bytes % 16
     assert cdll.dsl_moe_combine(p, 0, p, p, p, p, 4, 40, 16, 0, 4, p, 0, None) == -2                   # k > 32
+    ptrs = (ctypes.c_void_p * 2)(p, p)
+    assert cdll.dsl_moe_reduce_pull(ptrs, 17, 0, 4, 64, 1, p, 1, None) != 0                             # more ranks than DSL_MAX_PEERS
+    assert cdll.dsl_moe_reduce_pull(ptrs, 2, 0, 4, 60, 1, p, 1, None) == -2                            # row not whole 16-byte vectors
+    assert cdll.dsl_moe_reduce_pull(ptrs, 2, 0, 4, 64, 2, p, 1, None) == -4                            # fp16 shares
+    assert cdll.dsl_moe_reduce_pull((ctypes.c_void_p * 2)(p, None), 2, 0, 4, 64, 1, p, 1, None) == -1  # a missing peer buffer
+    assert cdll.dsl_moe_reduce_pull(ptrs, 2, 0, 0, 64, 1, p, 1, None) == 0                             # nothing to do
     assert cdll.dsl_quant_fp4_ref32(None, 0, 64, p, p, None) == -1
     assert cdll.dsl_gemm_fp4_ref32(p, p, p, p, p, 4, 8, 48, None) == -2                                # K % 32
