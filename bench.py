@@ -592,28 +592,33 @@ def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, 
 
     runner = run_eager
     graphs = None
+    steps_per_graph = None
     if graph:
-        # the same steps, captured once per input set and replayed: device time without host launch gaps
+        # the same steps captured eight at a time (over the rotating input sets) and replayed: device time without host
+        # launch gaps, and without charging every 17-us step a whole graph launch of its own - a decode step never runs
+        # as a graph by itself, it is one of the many small GEMMs of a layer stack
+        steps_per_graph = 8 if K >= 8 else K
+        K = max(steps_per_graph, K // steps_per_graph * steps_per_graph)
         side = torch.cuda.Stream()
-        graphs = []
         with torch.cuda.stream(side):
             for i in range(sets):
                 step(i)                               # this stream's scratch exists before capture
             torch.cuda.synchronize()
-            for i in range(sets):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    keep = step(i)
-                graphs.append((g, keep))
-            for i in range(W):
-                graphs[i % sets][0].replay()
+            g = torch.cuda.CUDAGraph()
+            keep = []
+            with torch.cuda.graph(g, stream=side):
+                for i in range(steps_per_graph):
+                    keep.append(step(i))
+            graphs = [(g, keep)]
+            for i in range(max(1, W // steps_per_graph)):
+                g.replay()
             torch.cuda.synchronize()
 
         def run_graph(n):
             side.wait_stream(torch.cuda.current_stream())      # the block's start event comes first
             with torch.cuda.stream(side):
-                for i in range(n):
-                    graphs[i % sets][0].replay()
+                for i in range(n // steps_per_graph):
+                    graphs[0][0].replay()
             torch.cuda.current_stream().wait_stream(side)
         runner = run_graph
 
@@ -657,7 +662,7 @@ def measure(name, args, timer, sampler, K, W, min_seconds, graph, strong, sets, 
         "burst": {"value": flops_all / (ms_blocks[0] * 1e-3) / 1e12, "ms_per_step": ms_blocks[0]},
         "repeats": len(ms_blocks), "steps": K, "timed_region_s": sum(times) / 1e3,
         "ms_per_step_min_median_max": [min(ms_blocks), ms_med, max(ms_blocks)],
-        "kernel_ms": gemm_ms_max, "quant_kernel_ms": quant_ms_max, "cuda_graph": bool(graph),
+        "kernel_ms": gemm_ms_max, "quant_kernel_ms": quant_ms_max, "cuda_graph": bool(graph), "steps_per_graph": steps_per_graph,
         "host_gap_ms": max(0.0, ms_med - gemm_ms_max - quant_ms_max),
     }
     if eager_ms is not None:
@@ -869,7 +874,7 @@ def main():
                     "how": "HostPipeline: pinned host buffers, copy-in / compute / copy-out on three streams, two staging buffers"},
             "host_us_per_call": host_us,
             "gpu_launches": head["gpu_launches"], "launches_per_step": head["launches_per_step"],
-            "cuda_graph": bool(args.graph),
+            "cuda_graph": bool(args.graph), "steps_per_graph": head.get("steps_per_graph"),
             "clocks": clocks if clocks is not None else (sampler.summary() if sampler is not None else None),
         }
         if "roofline_tensor" in head:
