@@ -19,7 +19,7 @@ _route_np = lambda logits, k, renorm: MO.route(logits, k, renorm)
 _plan_np = MO.plan
 
 
-@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (257, 64, 8), (100, 200, 5), (64, 1000, 32)])
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (9, 33, 4), (50, 40, 6), (257, 64, 8), (70, 65, 8), (100, 200, 5), (64, 1000, 32)])
 @pytest.mark.parametrize("renorm", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_route(cuda_device, T, E, k, renorm, dtype):
